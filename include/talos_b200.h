@@ -1,0 +1,224 @@
+/*
+ * talos_b200 -- C ABI of the B200 (sm_100a) implementation of the Talos-XII dense neural path.
+ *
+ * This is the surface a Rust `ffi.rs` (or any other FFI) binds.  Plain pointers and sizes only.
+ * All matrices are fp32, row-major, in DEVICE memory unless a parameter name ends in `_host`.
+ * Every function returns a talos_status (0 = OK), never throws across the boundary and never
+ * aborts; talos_last_error_string() gives the message of the calling thread's last failure.
+ * The reference crate reports the same conditions by panicking (assert!/assert_eq! on shapes,
+ * src/autograd.rs:96-100, :201, :209, :1611; src/nn.rs:187); a host shim turns a non-zero status
+ * back into a panic so GoodJobWorker::execute (src/worker.rs:110-132) still sees Err(String).
+ *
+ * Threading: a talos_ctx is one device + one stream; calls on one ctx must not overlap in time.
+ * Work is enqueued on the ctx stream; only *_host entry points and talos_ctx_synchronize block.
+ *
+ * Each declaration cites the reference item it replaces (paths are relative to the reference
+ * crate root).
+ */
+#ifndef TALOS_B200_H
+#define TALOS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t talos_status;
+enum {
+  TALOS_OK = 0,
+  TALOS_ERR_ARG = 1,      /* null pointer, bad enum, misaligned leading dimension */
+  TALOS_ERR_SHAPE = 2,    /* the reference's "dimension mismatch" panics */
+  TALOS_ERR_ALLOC = 3,
+  TALOS_ERR_CUDA = 4,
+  TALOS_ERR_NCCL = 5,
+  TALOS_ERR_TIMEOUT = 6,  /* a bounded device-side wait gave up; the context stays usable */
+  TALOS_ERR_UNSUPPORTED = 7
+};
+
+/* Arithmetic of the matrix products. */
+enum {
+  TALOS_MODE_FP32 = 0,    /* CUDA-core FFMA, fp32 exact products */
+  TALOS_MODE_TF32X3 = 1,  /* tcgen05 tensor cores, 3 TF32 products per term: fp32-faithful (<=1e-5) */
+  TALOS_MODE_TF32 = 2     /* tcgen05 tensor cores, single TF32 product: fast (<=2e-3) */
+};
+enum { TALOS_OP_N = 0, TALOS_OP_T = 1 };
+enum { TALOS_ACT_NONE = 0, TALOS_ACT_RELU = 1, TALOS_ACT_TANH = 2, TALOS_ACT_SILU = 3 };
+/* RoPE position convention. TOKEN: rotate by token position (src/transformer.rs:583-610).
+ * HEAD_INDEX: the autograd path's behaviour, which rotates a [B,S,H,dr] tensor by the index
+ * along its second-to-last axis, i.e. the head index (src/transformer.rs:262, :502-506). */
+enum { TALOS_ROPE_TOKEN = 0, TALOS_ROPE_HEAD_INDEX = 1 };
+
+typedef struct talos_ctx talos_ctx;
+
+/* ---- context ------------------------------------------------------------------------------ */
+/* `stream` is a cudaStream_t (NULL: the library creates its own non-blocking stream). */
+talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx** out);
+talos_status talos_ctx_destroy(talos_ctx* ctx);
+talos_status talos_ctx_synchronize(talos_ctx* ctx);
+talos_status talos_ctx_set_stream(talos_ctx* ctx, void* stream);
+/* Grow the ctx scratch buffer up front (split-K partials, dZ of Linear backward, attention
+ * probabilities) so that later calls do not allocate. */
+talos_status talos_ctx_reserve_workspace(talos_ctx* ctx, size_t bytes);
+const char* talos_last_error_string(void);
+/* 1 when the tcgen05 tensor-core GEMM passed its start-up self-check on this ctx and is in use
+ * for TF32 / TF32X3 modes; 0 when those modes are being served by the fp32 CUDA-core kernel. */
+int32_t talos_ctx_tensor_cores_active(talos_ctx* ctx);
+/* Number of kernels this library has launched on the ctx since creation. */
+int64_t talos_ctx_launch_count(talos_ctx* ctx);
+
+/* ---- GEMM: Tensor::matmul forward and both backward products ------------------------------ */
+/* Optional fused epilogue, applied in this order to acc = op(A).op(B):
+ *   v = acc + bias[n];  aux_out[m,n] = v;  v = act(v);  v *= dact(aux_in[m,n]);  C = v + beta*C.
+ * dact is the activation derivative expressed on the saved tensor: RELU/TANH take the saved
+ * OUTPUT y (y>0 ; 1-y^2), SILU takes the saved PRE-activation z. */
+typedef struct talos_epilogue {
+  const float* bias;      /* [N] or NULL: Linear's broadcast_to_batch + Add (src/nn.rs:102-117) */
+  float* aux_out;         /* [M,N] pre-activation save or NULL */
+  int64_t ld_aux_out;
+  const float* aux_in;    /* [M,N] tensor the derivative is evaluated on, or NULL */
+  int64_t ld_aux_in;
+  int32_t act;            /* TALOS_ACT_* applied to the result */
+  int32_t dact;           /* TALOS_ACT_* whose derivative multiplies the result */
+  int32_t beta;           /* 0: overwrite C; 1: C += (the reference's `+=` gradient accumulation,
+                             src/autograd.rs:304, :346) */
+} talos_epilogue;
+
+/* C[M,N] = op(A)[M,K] . op(B)[K,N].  op N: the operand is stored as written; op T: it is stored
+ * transposed (A as [K,M], B as [N,K]).  Replaces Tensor::matmul forward (opA=N, opB=N;
+ * src/autograd.rs:200-258), dLHS = G.B^T (opA=N, opB=T; :275-308) and dRHS = A^T.G
+ * (opA=T, opB=N; :310-350). */
+talos_status talos_gemm(talos_ctx* ctx, int32_t opA, int32_t opB, int64_t M, int64_t N, int64_t K,
+                        const float* A, int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc,
+                        int32_t mode, const talos_epilogue* epi);
+
+/* `batch` independent products with element strides between consecutive matrices.  Replaces
+ * batched_matmul_qt_k (opB=T; src/transformer.rs:877-958) and batched_matmul_probs_v
+ * (src/transformer.rs:961-1050) and their backward products. */
+talos_status talos_gemm_batched(talos_ctx* ctx, int32_t opA, int32_t opB, int64_t M, int64_t N, int64_t K,
+                                const float* A, int64_t lda, int64_t strideA, const float* B, int64_t ldb,
+                                int64_t strideB, float* C, int64_t ldc, int64_t strideC, int64_t batch,
+                                int32_t beta, int32_t mode);
+
+/* ---- Linear (src/nn.rs:12-142), weight [in,out] row-major, y = act(x.W + b) ---------------- */
+/* z_save (nullable) receives the pre-activation (needed by SILU backward). */
+talos_status talos_linear_fwd(talos_ctx* ctx, const float* x, const float* W, const float* bias, float* y,
+                              float* z_save, int64_t rows, int64_t in_features, int64_t out_features,
+                              int32_t act, int32_t mode);
+/* saved = y for RELU/TANH/NONE, z for SILU.  dx/dW/db may each be NULL.  accumulate bit0: dx +=,
+ * bit1: dW +=, bit2: db += (the reference always accumulates; fresh buffers pass 0). */
+talos_status talos_linear_bwd(talos_ctx* ctx, const float* x, const float* W, const float* saved,
+                              const float* dy, float* dx, float* dW, float* db, int64_t rows,
+                              int64_t in_features, int64_t out_features, int32_t act, int32_t mode,
+                              int32_t accumulate);
+/* broadcast_to_batch + Add and its backward column sum (src/autograd.rs:511-547). */
+talos_status talos_bias_add(talos_ctx* ctx, float* y, const float* bias, int64_t rows, int64_t n);
+talos_status talos_colsum(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n, int32_t accumulate);
+
+/* ---- RMSNorm (src/nn.rs:145-304): rms = sqrt(mean(x^2)+eps), y = x/rms*gamma --------------- */
+/* inv_rms [rows] is the only thing saved for backward (x-hat is recomputed). */
+talos_status talos_rmsnorm_fwd(talos_ctx* ctx, const float* x, const float* gamma, float eps, int64_t rows,
+                               int64_t dim, float* y, float* inv_rms);
+/* accumulate bit0: dx +=, bit1: dgamma +=. */
+talos_status talos_rmsnorm_bwd(talos_ctx* ctx, const float* dy, const float* x, const float* gamma,
+                               const float* inv_rms, int64_t rows, int64_t dim, float* dx, float* dgamma,
+                               int32_t accumulate);
+
+/* ---- RoPE (src/transformer.rs:220-371) ---------------------------------------------------- */
+/* cos/sin tables [max_len, dim/2] computed in f64 on the host as RoPE::precompute does
+ * (src/transformer.rs:239-251), rounded to fp32, written to device memory. */
+talos_status talos_rope_table(talos_ctx* ctx, int64_t dim, int64_t max_len, double base, float* cos_out,
+                              float* sin_out);
+/* x viewed as [outer, npos, inner, dim]; element (o,p,i,:) is rotated by position start_pos+p
+ * over interleaved pairs (2i,2i+1).  TOKEN on [B,S,H,dr]: outer=B,npos=S,inner=H.  HEAD_INDEX
+ * (RoPE::forward as the autograd path calls it): outer=B*S,npos=H,inner=1.  inverse=1 applies the
+ * transposed rotation (the backward, :319-331); accumulate=1 adds into y.  Positions at or past
+ * table_len are copied unrotated (src/transformer.rs:351, :586-588). */
+talos_status talos_rope(talos_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,
+                        int64_t table_len, int64_t outer, int64_t npos, int64_t inner, int64_t dim,
+                        int64_t start_pos, int32_t inverse, int32_t accumulate);
+
+/* ---- softmax (src/transformer.rs:1052-1121; src/simd.rs:333-359) -------------------------- */
+/* y = softmax(scale * x) over rows of length len.  causal_period > 0 (not in the reference):
+ * row r sees columns j <= r % causal_period. */
+talos_status talos_softmax_fwd(talos_ctx* ctx, const float* x, float* y, int64_t rows, int64_t len, float scale,
+                               int64_t causal_period);
+/* dx (+)= scale * y * (dy - sum_j dy_j y_j). */
+talos_status talos_softmax_bwd(talos_ctx* ctx, const float* y, const float* dy, float* dx, int64_t rows,
+                               int64_t len, float scale, int32_t accumulate);
+
+/* ---- attention core: scores -> scale -> softmax -> .V without writing scores to HBM -------- */
+/* q,k [BH,S,dqk], v [BH,S,dv], out [BH,S,dv]; probs (nullable) [BH,S,S] is written when the tape
+ * needs it.  Replaces batched_matmul_qt_k + scale_tensor + softmax + batched_matmul_probs_v
+ * (src/transformer.rs:539-550).  S <= 128. */
+talos_status talos_attention_fwd(talos_ctx* ctx, const float* q, const float* k, const float* v, float* out,
+                                 float* probs, int64_t BH, int64_t S, int64_t dqk, int64_t dv, float scale,
+                                 int32_t causal);
+/* Backward from saved probs: dq,dk,dv are overwritten. */
+talos_status talos_attention_bwd(talos_ctx* ctx, const float* q, const float* k, const float* v,
+                                 const float* probs, const float* dout, float* dq, float* dk, float* dv,
+                                 int64_t BH, int64_t S, int64_t dqk, int64_t dvdim, float scale);
+
+/* ---- layout ops --------------------------------------------------------------------------- */
+/* Tensor::transpose (src/autograd.rs:632-739): swap two axes of a rank<=6 tensor (full copy).
+ * accumulate=1 adds into y (its backward). `shape` is the INPUT shape, host memory. */
+talos_status talos_transpose(talos_ctx* ctx, const float* x, float* y, const int64_t* shape_host, int32_t rank,
+                             int32_t dim0, int32_t dim1, int32_t accumulate);
+/* concat_last_dim (src/transformer.rs:1123-1183) and its backward split. */
+talos_status talos_concat_last(talos_ctx* ctx, const float* a, const float* b, float* out, int64_t rows,
+                               int64_t da, int64_t db);
+talos_status talos_split_last(talos_ctx* ctx, const float* g, float* ga, float* gb, int64_t rows, int64_t da,
+                              int64_t db, int32_t accumulate);
+/* LuckTransformer::last_token (src/transformer.rs:92-109): [B,S,D] -> [B,D]. */
+talos_status talos_last_token(talos_ctx* ctx, const float* x, float* y, int64_t B, int64_t S, int64_t D);
+
+/* ---- elementwise + reductions (src/autograd.rs:356-509, :741-768, :1608-1862) ------------- */
+enum {
+  TALOS_EW_RELU = 1, TALOS_EW_TANH = 2, TALOS_EW_SILU = 3, TALOS_EW_EXP = 4, TALOS_EW_LOG = 5, TALOS_EW_SIN = 6,
+  TALOS_EW_COS = 7, TALOS_EW_SQRT = 8, TALOS_EW_CLIP = 9, TALOS_EW_NEG = 10, TALOS_EW_SCALE = 11,
+  TALOS_EW_ADD = 20, TALOS_EW_SUB = 21, TALOS_EW_MUL = 22, TALOS_EW_DIV = 23
+};
+/* y = f(x; p0, p1) (CLIP: min,max; SCALE: factor). */
+talos_status talos_eltwise_unary(talos_ctx* ctx, int32_t op, const float* x, float* y, int64_t n, float p0, float p1);
+/* dx += dy * f'(x)   (always accumulates, like the reference's closures). */
+talos_status talos_eltwise_unary_bwd(talos_ctx* ctx, int32_t op, const float* x, const float* dy, float* dx,
+                                     int64_t n, float p0, float p1);
+talos_status talos_eltwise_binary(talos_ctx* ctx, int32_t op, const float* a, const float* b, float* y, int64_t n);
+/* da += ..., db += ... for ADD/SUB/MUL/DIV; a and b (and da, db) may alias (x*x), which the
+ * reference special-cases at src/autograd.rs:1729, :1792. */
+talos_status talos_eltwise_binary_bwd(talos_ctx* ctx, int32_t op, const float* a, const float* b, const float* dy,
+                                      float* da, float* db, int64_t n);
+/* out[0] (+)= scale * sum(x): Tensor::sum / mean forward, broadcast backward. */
+talos_status talos_reduce_sum(talos_ctx* ctx, const float* x, int64_t n, float scale, float* out, int32_t accumulate);
+/* y[i] (+)= scale * s[0]: Tensor::broadcast forward, sum / mean backward. */
+talos_status talos_fill_from_scalar(talos_ctx* ctx, const float* s, float scale, float* y, int64_t n, int32_t accumulate);
+
+/* ---- PPO loss and Adam (src/ppo.rs) ------------------------------------------------------- */
+/* One pass over a minibatch of the per-sample loss of PPO::update (src/ppo.rs:702-755):
+ * log-softmax, ratio, clipped surrogate (surr1 iff surr1 < surr2), (v-R)^2, entropy; writes
+ * dL/dlogits [n,A] (row stride ld_out) and dL/dvalue, both already divided by `denom`, and ADDS
+ * {sum loss, sum kl, n} to stats[0..2].  values/dvalues have element stride `value_stride`. */
+talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logits, int64_t ld_logits, const float* values,
+                                    int64_t value_stride, const int32_t* actions, const float* old_logp,
+                                    const float* adv, const float* ret, int64_t n, int32_t n_actions, float clip,
+                                    float c_value, float c_entropy, float denom, float* dlogits, int64_t ld_out,
+                                    float* dvalues, int64_t dvalue_stride, float* stats);
+/* Adam::step over a flat buffer (src/ppo.rs:519-533): g is first multiplied by grad_scale;
+ * clip_norm > 0 adds the DQN optimizer's global-norm clip (src/dqn.rs:209-222). t is the step
+ * number after the increment (>= 1). */
+talos_status talos_adam_step(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
+                             int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
+                             float clip_norm);
+
+/* ---- seeded synthetic inputs: src/rng.rs:14-117 (SplitMix64 -> xoshiro256**) on the host ---- */
+talos_status talos_rng_uniform_host(uint64_t seed, float lo, float hi, float* out_host, int64_t n);
+talos_status talos_rng_normal_host(uint64_t seed, float mean, float std, float* out_host, int64_t n);
+talos_status talos_rng_bounded_host(uint64_t seed, uint32_t range, int32_t* out_host, int64_t n);
+/* Tensor::rand's LCG (src/autograd.rs:114-124), used by Linear::new (src/nn.rs:22-23). */
+talos_status talos_lcg_rand_host(uint64_t seed, double lo, double hi, double* out_host, int64_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TALOS_B200_H */

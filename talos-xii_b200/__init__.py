@@ -1,0 +1,169 @@
+"""talos_b200: Python host binding of libtalos_b200.so (the C ABI declared in include/*.h).
+
+The directory name is not a Python identifier; load it with `__graft_entry__.load_package()`
+(importlib by path, registered as module ``talos_xii_b200``).
+
+Every exported function of the headers is bound by parsing the headers themselves, so the
+binding cannot drift from the ABI.  A non-zero status raises `TalosError` carrying
+`talos_last_error_string()` -- the reference crate panics in the same situations.  There is
+no CPU path: loading the library or creating a context without a CUDA device fails loudly.
+"""
+import ctypes as C
+import os
+import re
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
+LIB_PATH = os.path.join(_HERE, "libtalos_b200.so")
+
+OK, ERR_ARG, ERR_SHAPE, ERR_ALLOC, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_UNSUPPORTED = range(8)
+MODE_FP32, MODE_TF32X3, MODE_TF32 = 0, 1, 2
+OP_N, OP_T = 0, 1
+ACT_NONE, ACT_RELU, ACT_TANH, ACT_SILU = 0, 1, 2, 3
+ROPE_TOKEN, ROPE_HEAD_INDEX = 0, 1
+EW = dict(relu=1, tanh=2, silu=3, exp=4, log=5, sin=6, cos=7, sqrt=8, clip=9, neg=10, scale=11, add=20, sub=21, mul=22, div=23)
+MODES = {"fp32": MODE_FP32, "tf32x3": MODE_TF32X3, "tf32": MODE_TF32}
+ACTS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "silu": 3}
+
+
+class TalosError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("talos status %d: %s" % (status, message))
+        self.status = status
+
+
+class Epilogue(C.Structure):
+    """Mirror of `talos_epilogue` (include/talos_b200.h)."""
+    _fields_ = [("bias", C.c_void_p), ("aux_out", C.c_void_p), ("ld_aux_out", C.c_int64), ("aux_in", C.c_void_p),
+                ("ld_aux_in", C.c_int64), ("act", C.c_int32), ("dact", C.c_int32), ("beta", C.c_int32)]
+
+
+_SCALARS = {"int32_t": C.c_int32, "int64_t": C.c_int64, "uint32_t": C.c_uint32, "uint64_t": C.c_uint64, "size_t": C.c_size_t,
+            "float": C.c_float, "double": C.c_double, "int": C.c_int, "talos_status": C.c_int32}
+
+
+def _ctype(decl):
+    decl = decl.replace("const", " ").strip()
+    stars = decl.count("*")
+    base = decl.replace("*", " ").split()
+    base = base[0] if base else "void"
+    if stars:
+        return C.c_void_p
+    return _SCALARS[base]
+
+
+def parse_headers(include_dir=INCLUDE_DIR):
+    """Returns {function name: (restype, [argtypes])} for every prototype in include/*.h."""
+    protos = {}
+    for fn in sorted(os.listdir(include_dir)):
+        if not fn.endswith(".h"):
+            continue
+        text = open(os.path.join(include_dir, fn)).read()
+        text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+        text = re.sub(r"//[^\n]*", " ", text)
+        text = re.sub(r"typedef\s+struct\s+\w+\s*\{.*?\}\s*\w+\s*;", " ", text, flags=re.S)
+        text = re.sub(r"enum\s*\{.*?\}\s*;", " ", text, flags=re.S)
+        for m in re.finditer(r"([\w\s\*]+?)\b(talos_\w+)\s*\(([^;{}]*?)\)\s*;", text):
+            ret, name, args = m.group(1).strip(), m.group(2), m.group(3).strip()
+            if "typedef" in ret:
+                continue
+            argtypes = []
+            if args and args != "void":
+                for a in args.split(","):
+                    a = a.strip()
+                    a = re.sub(r"\b\w+$", "", a).strip() if not a.endswith("*") else a   # drop the parameter name
+                    argtypes.append(_ctype(a))
+            if "char" in ret:
+                restype = C.c_char_p
+            else:
+                restype = _ctype(ret)
+            protos[name] = (restype, argtypes)
+    return protos
+
+
+class _Lib:
+    """Attribute access gives a checked callable: status != 0 raises TalosError."""
+
+    def __init__(self):
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("libtalos_b200.so is not built; run `python talos-xii_b200/build.py` "
+                              "(there is no CPU fallback)")
+        self.cdll = C.CDLL(LIB_PATH)
+        self.protos = parse_headers()
+        for name, (restype, argtypes) in self.protos.items():
+            f = getattr(self.cdll, name)
+            f.restype, f.argtypes = restype, argtypes
+
+    def raw(self, name):
+        return getattr(self.cdll, name)
+
+    def __getattr__(self, name):
+        protos = self.__dict__.get("protos", {})
+        if name not in protos:
+            raise AttributeError(name)
+        f = getattr(self.cdll, name)
+        if protos[name][0] is not C.c_int32 or not name.startswith("talos_") or name in _NOT_STATUS:
+            return f
+
+        def checked(*args):
+            st = f(*args)
+            if st != 0:
+                raise TalosError(st, self.cdll.talos_last_error_string().decode())
+        checked.__name__ = name
+        self.__dict__[name] = checked
+        return checked
+
+
+_NOT_STATUS = {"talos_ctx_tensor_cores_active"}
+
+lib = _Lib()
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor / numpy array / None as an int for ctypes."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    if hasattr(t, "ctypes"):
+        return t.ctypes.data
+    return int(t)
+
+
+class Context:
+    """One device + one stream (talos_ctx).  `stream` is a raw cudaStream_t value or None."""
+
+    def __init__(self, device=0, stream=None):
+        h = C.c_void_p()
+        lib.talos_ctx_create(int(device), stream, C.byref(h))
+        self.handle = h
+        self.device = device
+
+    def synchronize(self):
+        lib.talos_ctx_synchronize(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib.talos_ctx_destroy(self.handle)
+            self.handle = None
+
+    @property
+    def launches(self):
+        return lib.talos_ctx_launch_count(self.handle)
+
+    @property
+    def tensor_cores_active(self):
+        return bool(lib.talos_ctx_tensor_cores_active(self.handle))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def torch_context(device=0):
+    """A Context on torch's current stream for `device`, so torch allocations and copies order
+    with the library's kernels (torch is used for device memory and streams only)."""
+    import torch
+    return Context(device, torch.cuda.current_stream(device).cuda_stream)

@@ -1,0 +1,128 @@
+// Shared host-side plumbing for the talos_b200 library: context, error reporting, launch checks.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <atomic>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/talos_b200.h"
+
+#define TALOS_API extern "C" __attribute__((visibility("default")))
+
+struct talos_error : std::runtime_error {
+  talos_status code;
+  talos_error(talos_status c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+void talos_set_last_error(const std::string& msg);
+
+#define TALOS_CHECK_CUDA(expr)                                                                     \
+  do {                                                                                             \
+    cudaError_t e__ = (expr);                                                                      \
+    if (e__ != cudaSuccess)                                                                        \
+      throw talos_error(TALOS_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__));      \
+  } while (0)
+
+#define TALOS_REQUIRE(cond, code, msg)                                                             \
+  do {                                                                                             \
+    if (!(cond)) throw talos_error((code), std::string(msg) + " [" #cond "]");                     \
+  } while (0)
+
+// Wraps the body of every extern "C" entry point: exceptions become status codes.
+#define TALOS_ENTRY_BEGIN try {
+#define TALOS_ENTRY_END                                                                            \
+  return TALOS_OK;                                                                                 \
+  }                                                                                                \
+  catch (const talos_error& e) { talos_set_last_error(e.what()); return e.code; }                  \
+  catch (const std::bad_alloc&) { talos_set_last_error("host allocation failed"); return TALOS_ERR_ALLOC; } \
+  catch (const std::exception& e) { talos_set_last_error(e.what()); return TALOS_ERR_CUDA; }
+
+struct talos_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 148;
+  void* ws = nullptr;          // kernel-level scratch: split-K partials, column-sum / reduction partials
+  size_t ws_bytes = 0;
+  void* ws2 = nullptr;         // op-level scratch of composite entry points: dZ of Linear backward, dS of attention
+  size_t ws2_bytes = 0;
+  int32_t* dev_status = nullptr;   // device-side error word written by bounded waits
+  int tc_state = 0;            // tensor-core GEMM: 0 = not probed, 1 = active, -1 = disabled
+  std::atomic<int64_t> launches{0};
+  void* tmap_cache = nullptr;  // owned by gemm_tcgen05.cu
+};
+
+// Returns a scratch pointer of at least `bytes`, growing the buffer (stream-ordered free of the
+// old one) when needed.
+void* talos_workspace(talos_ctx* ctx, size_t bytes);
+// Same for the op-level scratch.  Composite entry points use this one so that the kernels they
+// call can take their own partial-sum scratch from talos_workspace without overlapping it.
+void* talos_workspace2(talos_ctx* ctx, size_t bytes);
+
+inline void talos_check_ctx(talos_ctx* ctx) {
+  TALOS_REQUIRE(ctx != nullptr, TALOS_ERR_ARG, "null context");
+  TALOS_CHECK_CUDA(cudaSetDevice(ctx->device));
+}
+
+// Call after every kernel launch.
+inline void talos_launched(talos_ctx* ctx, const char* what) {
+  ctx->launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw talos_error(TALOS_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- activation helpers shared by the GEMM epilogues and the elementwise kernels ----
+__device__ __forceinline__ float talos_act(float v, int act) {
+  switch (act) {
+    case TALOS_ACT_RELU: return v > 0.f ? v : 0.f;
+    case TALOS_ACT_TANH: return tanhf(v);
+    case TALOS_ACT_SILU: return v / (1.f + __expf(-v));
+    default: return v;
+  }
+}
+// Derivative evaluated on the saved tensor: the OUTPUT for relu/tanh, the PRE-activation for silu.
+__device__ __forceinline__ float talos_dact(float s, int act) {
+  switch (act) {
+    case TALOS_ACT_RELU: return s > 0.f ? 1.f : 0.f;
+    case TALOS_ACT_TANH: return 1.f - s * s;
+    case TALOS_ACT_SILU: { float g = 1.f / (1.f + __expf(-s)); return g * (1.f + s * (1.f - g)); }
+    default: return 1.f;
+  }
+}
+
+// Epilogue in device form (see talos_epilogue in the public header for the order of operations).
+struct EpiArgs {
+  const float* bias; float* aux_out; long long ld_aux_out; const float* aux_in; long long ld_aux_in;
+  int act; int dact; int beta;
+};
+inline EpiArgs talos_epi_args(const talos_epilogue* e) {
+  EpiArgs a{nullptr, nullptr, 0, nullptr, 0, 0, 0, 0};
+  if (e) { a.bias = e->bias; a.aux_out = e->aux_out; a.ld_aux_out = e->ld_aux_out; a.aux_in = e->aux_in;
+           a.ld_aux_in = e->ld_aux_in; a.act = e->act; a.dact = e->dact; a.beta = e->beta; }
+  return a;
+}
+__device__ __forceinline__ float talos_epilogue_apply(const EpiArgs& e, float acc, long long m, long long n,
+                                                      const float* C, long long ldc) {
+  float v = acc;
+  if (e.bias) v += __ldg(e.bias + n);
+  if (e.aux_out) e.aux_out[m * e.ld_aux_out + n] = v;
+  if (e.act) v = talos_act(v, e.act);
+  if (e.aux_in && e.dact) v *= talos_dact(__ldg(e.aux_in + m * e.ld_aux_in + n), e.dact);
+  if (e.beta) v += C[m * ldc + n];
+  return v;
+}
+
+// Internal cross-file entry points.
+void talos_gemm_fp32_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A,
+                            int64_t lda, int64_t strideA, const float* B, int64_t ldb, int64_t strideB, float* C,
+                            int64_t ldc, int64_t strideC, int64_t batch, const EpiArgs& epi);
+// Returns false when the shape/alignment is not eligible (caller falls back to the fp32 kernel).
+bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A,
+                          int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, int mode,
+                          const EpiArgs& epi);
+void talos_gemm_tc_release(talos_ctx* ctx);

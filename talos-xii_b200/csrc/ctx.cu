@@ -1,0 +1,149 @@
+// Context lifetime, scratch buffer, error string, seeded synthetic-input generators.
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+
+static thread_local std::string g_last_error;
+void talos_set_last_error(const std::string& msg) { g_last_error = msg; }
+
+TALOS_API const char* talos_last_error_string(void) { return g_last_error.c_str(); }
+
+static void* grow_scratch(talos_ctx* ctx, void** buf, size_t* have, size_t bytes) {
+  if (bytes <= *have) return *buf;
+  size_t want = bytes + (bytes >> 2);
+  want = (want + 255) & ~size_t(255);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, want);
+  if (e != cudaSuccess) { cudaGetLastError(); throw talos_error(TALOS_ERR_ALLOC, "workspace cudaMalloc failed"); }
+  if (*buf) { TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream)); cudaFree(*buf); }
+  *buf = p; *have = want;
+  return p;
+}
+void* talos_workspace(talos_ctx* ctx, size_t bytes) { return grow_scratch(ctx, &ctx->ws, &ctx->ws_bytes, bytes); }
+void* talos_workspace2(talos_ctx* ctx, size_t bytes) { return grow_scratch(ctx, &ctx->ws2, &ctx->ws2_bytes, bytes); }
+
+TALOS_API talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx** out) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(out != nullptr, TALOS_ERR_ARG, "null out pointer");
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) { cudaGetLastError(); throw talos_error(TALOS_ERR_CUDA, "no CUDA device: this library has no CPU path"); }
+  TALOS_REQUIRE(device >= 0 && device < count, TALOS_ERR_ARG, "device index out of range");
+  TALOS_CHECK_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  TALOS_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));
+  TALOS_REQUIRE(prop.major == 10, TALOS_ERR_UNSUPPORTED, "this library is built for sm_100a (B200) only");
+  talos_ctx* c = new talos_ctx();
+  c->device = device; c->sm_count = prop.multiProcessorCount;
+  if (stream) { c->stream = (cudaStream_t)stream; c->own_stream = false; }
+  else { TALOS_CHECK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)); c->own_stream = true; }
+  TALOS_CHECK_CUDA(cudaMalloc(&c->dev_status, 64));
+  TALOS_CHECK_CUDA(cudaMemset(c->dev_status, 0, 64));
+  *out = c;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ctx_destroy(talos_ctx* ctx) {
+  TALOS_ENTRY_BEGIN
+  if (!ctx) return TALOS_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  talos_gemm_tc_release(ctx);
+  if (ctx->ws) cudaFree(ctx->ws);
+  if (ctx->ws2) cudaFree(ctx->ws2);
+  if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ctx_synchronize(talos_ctx* ctx) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  int32_t st = 0;
+  TALOS_CHECK_CUDA(cudaMemcpy(&st, ctx->dev_status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(ctx->dev_status, 0, 64);
+    throw talos_error(TALOS_ERR_TIMEOUT, "a bounded device-side wait gave up (status " + std::to_string(st) + ")");
+  }
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ctx_set_stream(talos_ctx* ctx, void* stream) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(stream != nullptr, TALOS_ERR_ARG, "null stream");
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  ctx->stream = (cudaStream_t)stream; ctx->own_stream = false;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ctx_reserve_workspace(talos_ctx* ctx, size_t bytes) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  talos_workspace(ctx, bytes);
+  talos_workspace2(ctx, bytes);
+  TALOS_ENTRY_END
+}
+
+TALOS_API int32_t talos_ctx_tensor_cores_active(talos_ctx* ctx) { return ctx && ctx->tc_state == 1 ? 1 : 0; }
+TALOS_API int64_t talos_ctx_launch_count(talos_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
+
+// ---- src/rng.rs:14-117 restated: SplitMix64 seeding, xoshiro256**, 53-bit uniform, Box-Muller z0 ----
+namespace {
+struct Xoshiro {
+  uint64_t s[4];
+  explicit Xoshiro(uint64_t seed) {
+    for (int i = 0; i < 4; ++i) {
+      seed += 0x9e3779b97f4a7c15ULL; uint64_t z = seed;
+      z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL; z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL; s[i] = z ^ (z >> 31);
+    }
+  }
+  static uint64_t rotl(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
+  uint64_t next() {
+    uint64_t r = rotl(s[1] * 5, 7) * 9, t = s[1] << 17;
+    s[2] ^= s[0]; s[3] ^= s[1]; s[1] ^= s[2]; s[0] ^= s[3]; s[2] ^= t; s[3] = rotl(s[3], 45); return r;
+  }
+  double f64() { return (double)(next() >> 11) * (1.0 / 9007199254740992.0); }
+};
+}  // namespace
+
+TALOS_API talos_status talos_rng_uniform_host(uint64_t seed, float lo, float hi, float* out, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(out || n == 0, TALOS_ERR_ARG, "null output");
+  Xoshiro r(seed);
+  for (int64_t i = 0; i < n; ++i) out[i] = (float)((double)lo + ((double)hi - (double)lo) * r.f64());
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_rng_normal_host(uint64_t seed, float mean, float std, float* out, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(out || n == 0, TALOS_ERR_ARG, "null output");
+  Xoshiro r(seed);
+  for (int64_t i = 0; i < n; ++i) {
+    double u1; do { u1 = r.f64(); } while (!(u1 > 0.0));
+    double u2 = r.f64();
+    out[i] = (float)((double)mean + (double)std * (sqrt(-2.0 * log(u1)) * cos(2.0 * M_PI * u2)));
+  }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_rng_bounded_host(uint64_t seed, uint32_t range, int32_t* out, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(range > 0 && (out || n == 0), TALOS_ERR_ARG, "bad range or null output");
+  Xoshiro r(seed);
+  uint64_t rg = range, threshold = (0ULL - rg) % rg;
+  for (int64_t i = 0; i < n; ++i) { uint64_t x; do { x = r.next(); } while (x < threshold); out[i] = (int32_t)(x % rg); }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_lcg_rand_host(uint64_t seed, double lo, double hi, double* out, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(out || n == 0, TALOS_ERR_ARG, "null output");
+  uint64_t x = seed;
+  for (int64_t i = 0; i < n; ++i) {
+    x = x * 6364136223846793005ULL + 1ULL;
+    out[i] = lo + ((double)(x >> 33) / 4294967295.0) * (hi - lo);
+  }
+  TALOS_ENTRY_END
+}

@@ -1,0 +1,155 @@
+// PPO clipped-surrogate loss (forward + gradient in one pass) and the Adam optimizer step.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_ACTIONS = 64;
+
+// One thread per transition.  Restates the per-sample graph of PPO::update (src/ppo.rs:702-755):
+// max-subtracted log-softmax, ratio = exp(logp[a] - old), kl = (ratio-1) - log_ratio, surr1 is the
+// policy term iff surr1 < surr2, clip passes gradient on the closed interval, v_loss = (v-R)^2,
+// H = -sum p logp; loss = -policy + c_v v_loss - c_h H.  Gradients are divided by `denom`.
+template <int A>
+__global__ void __launch_bounds__(128)
+ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ values, long long vs,
+                const int* __restrict__ actions, const float* __restrict__ old_logp, const float* __restrict__ adv,
+                const float* __restrict__ ret, long long n, int n_actions, float clip, float c_v, float c_h, float inv_denom,
+                float* __restrict__ dlogits, long long ld_out, float* __restrict__ dvalues, long long dvs,
+                float* __restrict__ partial) {
+  __shared__ float sh_loss[128], sh_kl[128];
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float loss = 0.f, kl = 0.f;
+  if (i < n) {
+    const int na = A > 0 ? A : n_actions;
+    float l[A > 0 ? A : MAX_ACTIONS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int a = 0; a < na; ++a) { l[a] = logits[i * ld + a]; mx = fmaxf(mx, l[a]); }
+    float se = 0.f;
+#pragma unroll
+    for (int a = 0; a < na; ++a) se += expf(l[a] - mx);
+    const float lse = logf(se) + mx;
+    const int act = actions[i];
+    const float advantage = adv[i];
+    float ent = 0.f, lp_a = 0.f, sum_d = 0.f;
+#pragma unroll
+    for (int a = 0; a < na; ++a) {
+      float lp = l[a] - lse, p = expf(lp);
+      ent -= p * lp;
+      if (a == act) lp_a = lp;
+      l[a] = lp;
+    }
+    const float log_ratio = lp_a - old_logp[i], ratio = expf(log_ratio);
+    kl = (ratio - 1.f) - log_ratio;
+    const float lo = 1.f - clip, hi = 1.f + clip;
+    const float surr1 = ratio * advantage, surr2 = fminf(fmaxf(ratio, lo), hi) * advantage;
+    const bool use1 = surr1 < surr2;
+    const float policy = use1 ? surr1 : surr2;
+    const float d_ratio = use1 ? advantage : ((ratio >= lo && ratio <= hi) ? advantage : 0.f);
+    const float v = values[i * vs], dvl = v - ret[i];
+    loss = -policy + c_v * dvl * dvl - c_h * ent;
+    const float d_lp_a = -(d_ratio * ratio);
+    // d(loss)/d logp_j = c_h p_j (logp_j + 1) [+ d_lp_a at j = a]; logp = logits - lse
+#pragma unroll
+    for (int a = 0; a < na; ++a) {
+      float lp = l[a], p = expf(lp);
+      float d = c_h * p * (lp + 1.f) + (a == act ? d_lp_a : 0.f);
+      sum_d += d; l[a] = d;
+    }
+#pragma unroll
+    for (int a = 0; a < na; ++a) { float lp_p = expf(logits[i * ld + a] - lse); dlogits[i * ld_out + a] = (l[a] - lp_p * sum_d) * inv_denom; }
+    dvalues[i * dvs] = c_v * 2.f * dvl * inv_denom;
+  }
+  sh_loss[threadIdx.x] = loss; sh_kl[threadIdx.x] = kl; __syncthreads();
+  for (int o = 64; o > 0; o >>= 1) {
+    if (threadIdx.x < o) { sh_loss[threadIdx.x] += sh_loss[threadIdx.x + o]; sh_kl[threadIdx.x] += sh_kl[threadIdx.x + o]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { partial[2 * blockIdx.x] = sh_loss[0]; partial[2 * blockIdx.x + 1] = sh_kl[0]; }
+}
+
+// Sums the per-block (loss, kl) partials in block order and adds {loss, kl, n} to stats.
+__global__ void ppo_stats_kernel(const float* __restrict__ partial, int nblocks, float n, float* stats) {
+  __shared__ float sl[256], sk[256];
+  float a = 0.f, b = 0.f;
+  for (int i = threadIdx.x; i < nblocks; i += 256) { a += partial[2 * i]; b += partial[2 * i + 1]; }
+  sl[threadIdx.x] = a; sk[threadIdx.x] = b; __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) { sl[threadIdx.x] += sl[threadIdx.x + o]; sk[threadIdx.x] += sk[threadIdx.x + o]; } __syncthreads(); }
+  if (threadIdx.x == 0) { stats[0] += sl[0]; stats[1] += sk[0]; stats[2] += n; }
+}
+
+__global__ void sumsq_stage1_kernel(const float* __restrict__ g, long long n, float scale, float* __restrict__ partial) {
+  __shared__ float sh[256];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) { float v = g[i] * scale; s += v * v; }
+  sh[threadIdx.x] = s; __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o]; __syncthreads(); }
+  if (threadIdx.x == 0) partial[blockIdx.x] = sh[0];
+}
+
+// Adam::step (src/ppo.rs:519-533).  norm_partial != null: DQN's global-norm clip (src/dqn.rs:209-222);
+// every thread re-sums the (few) block partials in the same order, so the result is deterministic.
+__global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                            long long n, float lr, float b1, float b2, float eps, float inv_bc1, float inv_bc2,
+                            float grad_scale, const float* __restrict__ norm_partial, int nparts, float clip_norm) {
+  float coef = grad_scale;
+  if (norm_partial) {
+    float tot = 0.f;
+    for (int i = 0; i < nparts; ++i) tot += norm_partial[i];
+    tot = sqrtf(tot);
+    if (tot > clip_norm) coef *= clip_norm / tot;
+  }
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float gi = g[i] * coef;
+  float mi = b1 * m[i] + (1.f - b1) * gi;
+  float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  m[i] = mi; v[i] = vi;
+  p[i] -= lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+}
+
+}  // namespace
+
+TALOS_API talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logits, int64_t ld_logits, const float* values,
+                                              int64_t value_stride, const int32_t* actions, const float* old_logp,
+                                              const float* adv, const float* ret, int64_t n, int32_t n_actions, float clip,
+                                              float c_value, float c_entropy, float denom, float* dlogits, int64_t ld_out,
+                                              float* dvalues, int64_t dvalue_stride, float* stats) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(n >= 0 && n_actions >= 1 && n_actions <= MAX_ACTIONS, TALOS_ERR_SHAPE, "1..64 actions supported");
+  TALOS_REQUIRE(ld_logits >= n_actions && ld_out >= n_actions && denom > 0.f, TALOS_ERR_SHAPE, "bad leading dimension or denominator");
+  if (n == 0) return TALOS_OK;
+  TALOS_REQUIRE(logits && values && actions && old_logp && adv && ret && dlogits && dvalues && stats, TALOS_ERR_ARG, "null pointer");
+  int blocks = (int)ceil_div(n, 128);
+  float* partial = (float*)talos_workspace(ctx, sizeof(float) * 2 * (size_t)blocks);
+#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial)
+  if (n_actions == 16) TALOS_PPO_LAUNCH(16); else if (n_actions == 5) TALOS_PPO_LAUNCH(5); else TALOS_PPO_LAUNCH(0);
+#undef TALOS_PPO_LAUNCH
+  talos_launched(ctx, "ppo_loss");
+  ppo_stats_kernel<<<1, 256, 0, ctx->stream>>>(partial, blocks, (float)n, stats);
+  talos_launched(ctx, "ppo_stats");
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_adam_step(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
+                                       int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
+                                       float clip_norm) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(n >= 0 && t >= 1, TALOS_ERR_ARG, "Adam step number must be >= 1");
+  if (n == 0) return TALOS_OK;
+  TALOS_REQUIRE(params && grads && m && v, TALOS_ERR_ARG, "null pointer");
+  const double bc1 = 1.0 - pow((double)beta1, (double)t), bc2 = 1.0 - pow((double)beta2, (double)t);
+  float* norm_partial = nullptr; int nparts = 0;
+  if (clip_norm > 0.f) {
+    nparts = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(n, 4096), 64));
+    norm_partial = (float*)talos_workspace(ctx, sizeof(float) * nparts);
+    sumsq_stage1_kernel<<<nparts, 256, 0, ctx->stream>>>(grads, n, grad_scale, norm_partial);
+    talos_launched(ctx, "adam_sumsq");
+  }
+  adam_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(params, grads, m, v, n, lr, beta1, beta2, eps, (float)(1.0 / bc1),
+                                                                  (float)(1.0 / bc2), grad_scale, norm_partial, nparts, clip_norm);
+  talos_launched(ctx, "adam");
+  TALOS_ENTRY_END
+}

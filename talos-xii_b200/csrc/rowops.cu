@@ -1,0 +1,336 @@
+// Memory-bound row kernels: RMSNorm, softmax, RoPE.  One warp per row, 128-bit loads, the row
+// held in registers between the reduction and the rescale, warp-shuffle reductions.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS_PER_CTA = 8;
+constexpr int MAX_VEC = 8;                 // 8 float4 per lane -> rows up to 1024 floats in registers
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---------------------------------------------------------------- RMSNorm forward
+// y = x * rsqrt(mean(x^2) + eps) * gamma; saves inv_rms per row.
+template <int NVEC>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+rmsnorm_fwd_vec_kernel(const float4* __restrict__ x, const float4* __restrict__ gamma, float eps, long long rows,
+                       int dim4, float* __restrict__ inv_rms, float4* __restrict__ y) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  float4 gam[NVEC];
+#pragma unroll
+  for (int v = 0; v < NVEC; ++v) { int c = lane + v * 32; gam[v] = c < dim4 ? __ldg(gamma + c) : make_float4(0, 0, 0, 0); }
+  for (long long r = warp; r < rows; r += nwarps) {
+    const float4* xr = x + r * dim4;
+    float4 xv[NVEC]; float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < NVEC; ++v) {
+      int c = lane + v * 32;
+      xv[v] = c < dim4 ? __ldcs(xr + c) : make_float4(0, 0, 0, 0);
+      ss += xv[v].x * xv[v].x + xv[v].y * xv[v].y + xv[v].z * xv[v].z + xv[v].w * xv[v].w;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)(dim4 * 4) + eps);
+    if (lane == 0 && inv_rms) inv_rms[r] = inv;
+    float4* yr = y + r * dim4;
+#pragma unroll
+    for (int v = 0; v < NVEC; ++v) {
+      int c = lane + v * 32;
+      if (c < dim4) {
+        float4 o; o.x = xv[v].x * inv * gam[v].x; o.y = xv[v].y * inv * gam[v].y;
+        o.z = xv[v].z * inv * gam[v].z; o.w = xv[v].w * inv * gam[v].w;
+        __stcs(yr + c, o);
+      }
+    }
+  }
+}
+
+// Any dim / alignment: one warp per row, scalar strided loop, row re-read from cache.
+__global__ void rmsnorm_fwd_generic_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float eps,
+                                           long long rows, int dim, float* __restrict__ inv_rms, float* __restrict__ y) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const float* xr = x + r * dim; float ss = 0.f;
+    for (int c = lane; c < dim; c += 32) ss += xr[c] * xr[c];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    if (lane == 0 && inv_rms) inv_rms[r] = inv;
+    for (int c = lane; c < dim; c += 32) y[r * dim + c] = xr[c] * inv * gamma[c];
+  }
+}
+
+// ---------------------------------------------------------------- RMSNorm backward
+// dx (+)= inv*(dy*g - xhat*mean(dy*g*xhat)); per-CTA column partials of dy*xhat go to `partial`
+// [gridDim.x][dim] and are summed in block order by colsum_partials_kernel (deterministic).
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+rmsnorm_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
+                   const float* __restrict__ inv_rms, long long rows, int dim, float* __restrict__ dx, int acc_dx,
+                   float* __restrict__ partial) {
+  extern __shared__ float sh[];            // [WARPS_PER_CTA][dim] column partials
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  float* mine = sh + (size_t)w * dim;
+  for (int c = lane; c < dim; c += 32) mine[c] = 0.f;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + w;
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const float inv = inv_rms[r];
+    const float* dyr = dy + r * dim; const float* xr = x + r * dim;
+    float dot = 0.f;
+    for (int c = lane; c < dim; c += 32) dot += dyr[c] * gamma[c] * (xr[c] * inv);
+    dot = warp_sum(dot) / (float)dim;
+    for (int c = lane; c < dim; c += 32) {
+      float g = dyr[c], xh = xr[c] * inv;
+      if (dx) { float v = inv * (g * gamma[c] - xh * dot); dx[r * dim + c] = acc_dx ? dx[r * dim + c] + v : v; }
+      mine[c] += g * xh;
+    }
+  }
+  __syncthreads();
+  if (partial)
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      float s = 0.f;
+      for (int i = 0; i < WARPS_PER_CTA; ++i) s += sh[(size_t)i * dim + c];
+      partial[(size_t)blockIdx.x * dim + c] = s;
+    }
+}
+
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, int nparts, int dim, float* __restrict__ out, int acc) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * dim + c];
+  out[c] = acc ? out[c] + s : s;
+}
+
+// Column sums of a [rows, n] matrix, stage 1: each CTA sums a contiguous slab of rows.
+__global__ void colsum_stage1_kernel(const float* __restrict__ g, long long rows, int n, long long rows_per_cta,
+                                     float* __restrict__ partial) {
+  long long r0 = (long long)blockIdx.y * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  float s = 0.f;
+  for (long long r = r0; r < r1; ++r) s += g[r * n + c];
+  partial[(size_t)blockIdx.y * n + c] = s;
+}
+
+// ---------------------------------------------------------------- softmax
+// y = softmax(scale*x) over a row of `len` <= 32*NPL, one warp per row.
+template <int NPL>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+softmax_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, int len, float scale, int causal_period) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const int lim = causal_period > 0 ? (int)(r % causal_period) + 1 : len;
+    float v[NPL]; float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      int c = lane + i * 32;
+      v[i] = c < lim ? __ldcs(x + r * len + c) * scale : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) { v[i] = (lane + i * 32) < lim ? expf(v[i] - mx) : 0.f; sum += v[i]; }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) { int c = lane + i * 32; if (c < len) __stcs(y + r * len + c, v[i] * inv); }
+  }
+}
+
+template <int NPL>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+softmax_bwd_kernel(const float* __restrict__ y, const float* dy, float* dx, long long rows,
+                   int len, float scale, int acc) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  for (long long r = warp; r < rows; r += nwarps) {
+    float yv[NPL], gv[NPL]; float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      int c = lane + i * 32;
+      yv[i] = c < len ? __ldcs(y + r * len + c) : 0.f; gv[i] = c < len ? dy[r * len + c] : 0.f;   // dy may alias dx
+      s += yv[i] * gv[i];
+    }
+    s = warp_sum(s);
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      int c = lane + i * 32;
+      if (c < len) { float v = scale * yv[i] * (gv[i] - s); dx[r * len + c] = acc ? dx[r * len + c] + v : v; }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- RoPE
+// One thread per interleaved pair (2i, 2i+1) of a [outer, npos, inner, dim] tensor.
+__global__ void rope_kernel(const float2* __restrict__ x, float2* __restrict__ y, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, long long table_len, long long total_pairs, int npos,
+                            int inner, int half, long long start_pos, int inverse, int acc) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_pairs) return;
+  int i = (int)(idx % half);
+  long long rest = idx / half;               // (o*npos + p)*inner + in
+  long long p = (rest / inner) % npos;
+  long long toff = (start_pos + p) * half;
+  float2 v = x[idx], o;
+  if (toff >= table_len) { o = v; }
+  else {
+    float c = __ldg(cos_t + toff + i), s = __ldg(sin_t + toff + i);
+    if (inverse) s = -s;
+    o.x = v.x * c - v.y * s; o.y = v.x * s + v.y * c;
+  }
+  if (acc) { float2 old = y[idx]; o.x += old.x; o.y += old.y; }
+  y[idx] = o;
+}
+
+int row_grid(talos_ctx* ctx, int64_t rows) {
+  int64_t want = ceil_div(rows, WARPS_PER_CTA);
+  int64_t cap = (int64_t)ctx->sm_count * 8;          // 8 resident CTAs of 256 threads per SM
+  return (int)std::max<int64_t>(1, std::min(want, cap));
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+
+TALOS_API talos_status talos_rmsnorm_fwd(talos_ctx* ctx, const float* x, const float* gamma, float eps, int64_t rows,
+                                         int64_t dim, float* y, float* inv_rms) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(rows >= 0 && dim > 0 && dim < (1 << 24), TALOS_ERR_SHAPE, "RMSNorm dim mismatch");
+  if (rows == 0) return TALOS_OK;
+  TALOS_REQUIRE(x && gamma && y, TALOS_ERR_ARG, "null pointer");
+  int grid = row_grid(ctx, rows);
+  if (dim % 4 == 0 && dim <= 32 * 4 * MAX_VEC && aligned16(x) && aligned16(y) && aligned16(gamma)) {
+    int dim4 = (int)(dim / 4), nvec = (int)ceil_div(dim4, 32);
+    auto X = (const float4*)x; auto G = (const float4*)gamma; auto Y = (float4*)y;
+#define TALOS_RMS_CASE(NV) case NV: rmsnorm_fwd_vec_kernel<NV><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(X, G, eps, rows, dim4, inv_rms, Y); break;
+    switch (nvec) { TALOS_RMS_CASE(1) TALOS_RMS_CASE(2) TALOS_RMS_CASE(3) TALOS_RMS_CASE(4) TALOS_RMS_CASE(5) TALOS_RMS_CASE(6) TALOS_RMS_CASE(7) TALOS_RMS_CASE(8) }
+#undef TALOS_RMS_CASE
+  } else {
+    rmsnorm_fwd_generic_kernel<<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, gamma, eps, rows, (int)dim, inv_rms, y);
+  }
+  talos_launched(ctx, "rmsnorm_fwd");
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_rmsnorm_bwd(talos_ctx* ctx, const float* dy, const float* x, const float* gamma,
+                                         const float* inv_rms, int64_t rows, int64_t dim, float* dx, float* dgamma,
+                                         int32_t accumulate) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(rows >= 0 && dim > 0 && dim <= 1536, TALOS_ERR_SHAPE, "RMSNorm backward supports dim <= 1536");
+  if (rows == 0) return TALOS_OK;
+  TALOS_REQUIRE(dy && x && gamma && inv_rms, TALOS_ERR_ARG, "null pointer");
+  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, WARPS_PER_CTA), (int64_t)ctx->sm_count * 4));
+  float* partial = dgamma ? (float*)talos_workspace(ctx, sizeof(float) * (size_t)grid * dim) : nullptr;
+  size_t shmem = sizeof(float) * WARPS_PER_CTA * (size_t)dim;
+  rmsnorm_bwd_kernel<<<grid, WARPS_PER_CTA * 32, shmem, ctx->stream>>>(dy, x, gamma, inv_rms, rows, (int)dim, dx,
+                                                                        accumulate & 1, partial);
+  talos_launched(ctx, "rmsnorm_bwd");
+  if (dgamma) {
+    colsum_partials_kernel<<<(unsigned)ceil_div(dim, 128), 128, 0, ctx->stream>>>(partial, grid, (int)dim, dgamma, (accumulate >> 1) & 1);
+    talos_launched(ctx, "rmsnorm_dgamma");
+  }
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_colsum(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n, int32_t accumulate) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(rows >= 0 && n > 0 && n < (1 << 24), TALOS_ERR_SHAPE, "bad colsum shape");
+  TALOS_REQUIRE(g && out, TALOS_ERR_ARG, "null pointer");
+  int64_t col_blocks = ceil_div(n, 128);
+  int64_t slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 64), (4 * (int64_t)ctx->sm_count) / col_blocks + 1));
+  int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
+  float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
+  colsum_stage1_kernel<<<dim3((unsigned)col_blocks, (unsigned)slabs), 128, 0, ctx->stream>>>(g, rows, (int)n, rows_per, partial);
+  talos_launched(ctx, "colsum_stage1");
+  colsum_partials_kernel<<<(unsigned)col_blocks, 128, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
+  talos_launched(ctx, "colsum_stage2");
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_softmax_fwd(talos_ctx* ctx, const float* x, float* y, int64_t rows, int64_t len, float scale,
+                                         int64_t causal_period) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(rows >= 0 && len >= 0 && len <= 1024, TALOS_ERR_SHAPE, "softmax row length must be <= 1024");
+  if (rows == 0 || len == 0) return TALOS_OK;       // an empty row sums to 0 (src/simd.rs:335-337)
+  TALOS_REQUIRE(x && y, TALOS_ERR_ARG, "null pointer");
+  int grid = row_grid(ctx, rows); int npl = (int)ceil_div(len, 32);
+#define TALOS_SM_CASE(NP) if (npl <= NP) softmax_fwd_kernel<NP><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, (int)len, scale, (int)causal_period); else
+  TALOS_SM_CASE(1) TALOS_SM_CASE(2) TALOS_SM_CASE(4) TALOS_SM_CASE(8) TALOS_SM_CASE(16)
+  softmax_fwd_kernel<32><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, (int)len, scale, (int)causal_period);
+#undef TALOS_SM_CASE
+  talos_launched(ctx, "softmax_fwd");
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_softmax_bwd(talos_ctx* ctx, const float* y, const float* dy, float* dx, int64_t rows,
+                                         int64_t len, float scale, int32_t accumulate) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(rows >= 0 && len >= 0 && len <= 1024, TALOS_ERR_SHAPE, "softmax row length must be <= 1024");
+  if (rows == 0 || len == 0) return TALOS_OK;
+  TALOS_REQUIRE(y && dy && dx, TALOS_ERR_ARG, "null pointer");
+  int grid = row_grid(ctx, rows); int npl = (int)ceil_div(len, 32); int acc = accumulate ? 1 : 0;
+#define TALOS_SM_CASE(NP) if (npl <= NP) softmax_bwd_kernel<NP><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(y, dy, dx, rows, (int)len, scale, acc); else
+  TALOS_SM_CASE(1) TALOS_SM_CASE(2) TALOS_SM_CASE(4) TALOS_SM_CASE(8) TALOS_SM_CASE(16)
+  softmax_bwd_kernel<32><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(y, dy, dx, rows, (int)len, scale, acc);
+#undef TALOS_SM_CASE
+  talos_launched(ctx, "softmax_bwd");
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_rope_table(talos_ctx* ctx, int64_t dim, int64_t max_len, double base, float* cos_out,
+                                        float* sin_out) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(dim > 0 && dim % 2 == 0 && max_len >= 0, TALOS_ERR_SHAPE, "RoPE dim must be even");
+  TALOS_REQUIRE(cos_out && sin_out, TALOS_ERR_ARG, "null pointer");
+  int64_t h = dim / 2; size_t n = (size_t)(max_len * h);
+  std::string buf(sizeof(float) * 2 * n, '\0');
+  float* hc = (float*)&buf[0]; float* hs = hc + n;
+  for (int64_t pos = 0; pos < max_len; ++pos)
+    for (int64_t i = 0; i < h; ++i) {
+      double theta = 1.0 / pow(base, (double)(2 * i) / (double)dim), ang = (double)pos * theta;
+      hc[pos * h + i] = (float)cos(ang); hs[pos * h + i] = (float)sin(ang);
+    }
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(cos_out, hc, sizeof(float) * n, cudaMemcpyHostToDevice, ctx->stream));
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(sin_out, hs, sizeof(float) * n, cudaMemcpyHostToDevice, ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));     // the staging buffer dies with this call
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_rope(talos_ctx* ctx, const float* x, float* y, const float* cos_t, const float* sin_t,
+                                  int64_t table_len, int64_t outer, int64_t npos, int64_t inner, int64_t dim,
+                                  int64_t start_pos, int32_t inverse, int32_t accumulate) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(dim > 0 && dim % 2 == 0 && outer >= 0 && npos >= 0 && inner >= 0 && start_pos >= 0, TALOS_ERR_SHAPE, "bad RoPE shape");
+  int64_t pairs = outer * npos * inner * (dim / 2);
+  if (pairs == 0) return TALOS_OK;
+  TALOS_REQUIRE(x && y && cos_t && sin_t, TALOS_ERR_ARG, "null pointer");
+  TALOS_REQUIRE(((uintptr_t)x & 7) == 0 && ((uintptr_t)y & 7) == 0, TALOS_ERR_ARG, "RoPE buffers must be 8-byte aligned");
+  rope_kernel<<<(unsigned)ceil_div(pairs, 256), 256, 0, ctx->stream>>>((const float2*)x, (float2*)y, cos_t, sin_t, table_len,
+                                                                        pairs, (int)npos, (int)inner, (int)(dim / 2), start_pos,
+                                                                        inverse ? 1 : 0, accumulate ? 1 : 0);
+  talos_launched(ctx, "rope");
+  TALOS_ENTRY_END
+}
