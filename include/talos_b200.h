@@ -53,7 +53,7 @@ enum { TALOS_ROPE_TOKEN = 0, TALOS_ROPE_HEAD_INDEX = 1 };
 typedef struct talos_ctx talos_ctx;
 
 /* ---- context ------------------------------------------------------------------------------ */
-/* `stream` is a cudaStream_t (NULL: the library creates its own non-blocking stream). */
+/* `stream` is the cudaStream_t all work of this ctx is enqueued on (NULL: the default stream). */
 talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx** out);
 talos_status talos_ctx_destroy(talos_ctx* ctx);
 talos_status talos_ctx_synchronize(talos_ctx* ctx);

@@ -36,8 +36,7 @@ TALOS_API talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx*
   TALOS_REQUIRE(prop.major == 10, TALOS_ERR_UNSUPPORTED, "this library is built for sm_100a (B200) only");
   talos_ctx* c = new talos_ctx();
   c->device = device; c->sm_count = prop.multiProcessorCount;
-  if (stream) { c->stream = (cudaStream_t)stream; c->own_stream = false; }
-  else { TALOS_CHECK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)); c->own_stream = true; }
+  c->stream = (cudaStream_t)stream; c->own_stream = false;     // NULL is the device's default stream
   TALOS_CHECK_CUDA(cudaMalloc(&c->dev_status, 64));
   TALOS_CHECK_CUDA(cudaMemset(c->dev_status, 0, 64));
   *out = c;
@@ -74,7 +73,6 @@ TALOS_API talos_status talos_ctx_synchronize(talos_ctx* ctx) {
 TALOS_API talos_status talos_ctx_set_stream(talos_ctx* ctx, void* stream) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
-  TALOS_REQUIRE(stream != nullptr, TALOS_ERR_ARG, "null stream");
   TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   ctx->stream = (cudaStream_t)stream; ctx->own_stream = false;

@@ -1,5 +1,479 @@
-// placeholder until the tcgen05 kernel lands
+// Tensor-core GEMM for sm_100a: tcgen05.mma (kind::tf32) with accumulators in TMEM, operands staged
+// in 128B-swizzled shared memory by TMA (no multicast), mbarrier pipeline, warp-specialised roles,
+// persistent tile loop with a double-buffered TMEM accumulator so the epilogue of one tile overlaps
+// the main loop of the next.
+//
+//   TALOS_MODE_TF32   one TF32 product per term (operands truncated to TF32 by the tensor core).
+//   TALOS_MODE_TF32X3 a converter warpgroup splits every fp32 tile in shared memory into
+//                     hi = tf32(a) and lo = tf32(a - hi) and the issuer runs lo.hi + hi.lo + hi.hi
+//                     into the same accumulator (small terms first): fp32-faithful results.
+//
+// All four operand layouts are handled by descriptor major-ness (K-major / MN-major), so
+// A.B, A.B^T and A^T.B need no transpose pass.  Every wait on an mbarrier is bounded; when one
+// gives up the CTA raises an error word, drains, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
+
 #include "common.cuh"
-bool talos_gemm_tc_launch(talos_ctx*, int, int, int64_t, int64_t, int64_t, const float*, int64_t, const float*, int64_t,
-                          float*, int64_t, int, const EpiArgs&) { return false; }
+
+void talos_splitk_reduce(talos_ctx* ctx, const float* partial, int splits, int64_t M, int64_t N, float* C,
+                         int64_t ldc, const EpiArgs& epi);
+
+namespace {
+
+constexpr int BM = 128;                 // tile rows = TMEM lanes
+constexpr int BK = 32;                  // fp32 per 128-byte swizzle row
+constexpr int UMMA_K = 8;               // K per tcgen05.mma.kind::tf32
+constexpr uint32_t WAIT_SPINS = 1u << 22;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after raising *abort_flag) when the barrier never flips or when
+// another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) { if (*abort_flag) return false; __nanosleep(i > 4096 ? 256 : 32); }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cvt_tf32(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return r; }
+
+// Shared-memory matrix descriptor for a swizzled operand tile (1024-byte aligned).
+//  K-major : layout 2 (128B swizzle, 16-byte atoms): rows of 128 B, 8-row groups 1024 B apart (SBO);
+//            the leading offset is unused (1).
+//  MN-major: fp32 operands must use layout 1 (128B swizzle with 32-byte atoms, 4-row period):
+//            32-float column chunks, each [BK rows][128 B]; chunk stride (LBO) = BK*128 B,
+//            4-row k-groups 512 B apart (SBO).  TMA writes it with SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;                  // descriptor version for this architecture
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+struct TcArgs {
+  int M, N, K;
+  int m_tiles, n_tiles, splits, kb_total, kb_per_split;
+  float* C; long long ldc;
+  float* partial;                          // [splits][M][N] when splits > 1
+  EpiArgs epi;
+  int32_t* status;
+};
+
+// Shared storage layout (dynamic, 1024-byte aligned):
+//   [STAGES][A tile (hi)] [STAGES][B tile (hi)] ([STAGES][A lo] [STAGES][B lo] in X3 mode) barriers...
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(X3 ? 320 : 192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcArgs g) {
+  constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
+  constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + STAGES * A_BYTES;
+  uint8_t* sAlo = sB + STAGES * B_BYTES;
+  uint8_t* sBlo = sAlo + (X3 ? STAGES * A_BYTES : 0);
+  uint64_t* bars = (uint64_t*)(sBlo + (X3 ? STAGES * B_BYTES : 0));
+  uint64_t* full = bars;                   // TMA -> (converter | issuer)
+  uint64_t* conv = full + STAGES;          // converter -> issuer (X3)
+  uint64_t* empty = conv + STAGES;         // issuer (commit) -> TMA
+  uint64_t* tfull = empty + STAGES;        // issuer (commit) -> epilogue, per accumulator buffer
+  uint64_t* tempty = tfull + 2;            // epilogue -> issuer
+  uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, 4); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_mn = g.m_tiles * g.n_tiles;
+  const int items = tiles_mn * g.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b);
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+        const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+        const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(full + stage, A_BYTES + B_BYTES);
+          uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
+          if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, mb * BM + 32 * j, kb * BK, full + stage); }
+          else tma_load_2d(a_dst, &tmap_a, kb * BK, mb * BM, full + stage);
+          if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, nb * BN + 32 * j, kb * BK, full + stage); }
+          else tma_load_2d(b_dst, &tmap_b, kb * BK, nb * BN, full + stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t a_lbo = A_MN ? BK * 128 : 16, b_lbo = B_MN ? BK * 128 : 16;
+      const uint32_t a_kstep = A_MN ? 1024 : UMMA_K * 4, b_kstep = B_MN ? 1024 : UMMA_K * 4;
+      const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024, a_lay = A_MN ? 1 : 2, b_lay = B_MN ? 1 : 2;
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
+      for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+        const int ks = it / tiles_mn;
+        const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
+        if (!mbar_wait(tempty + acc, acc_phase[acc] ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait((X3 ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
+            if (X3) {
+              const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
+              const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
+              tc_mma_tf32(d_tmem, dal, db, idesc, accum);      // lo.hi
+              tc_mma_tf32(d_tmem, da, dbl, idesc, 1u);         // hi.lo
+              tc_mma_tf32(d_tmem, da, db, idesc, 1u);          // hi.hi
+            } else {
+              tc_mma_tf32(d_tmem, da, db, idesc, accum);
+            }
+          }
+          tc_commit(empty + stage);                            // frees the stage when these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(tfull + acc);                                // accumulator complete
+        acc_phase[acc] ^= 1; acc ^= 1;
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------- epilogue (4 warps, one TMEM lane quadrant each)
+    const int quad = warp & 3;
+    int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
+    for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+      const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+      if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const long long m = (long long)mb * BM + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+      const bool row_ok = m < g.M;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const long long n0 = (long long)nb * BN + c0;
+        if (n0 >= g.N) break;                                  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(t_row + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          if (g.splits > 1) {
+            float* P = g.partial + ((long long)ks * g.M + m) * g.N + n0;
+            const bool vec = (n0 + 32 <= g.N) && ((((uintptr_t)P) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *(float4*)(P + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32; ++j) if (n0 + j < g.N) P[j] = __uint_as_float(r[j]);
+            }
+          } else {
+            float* Crow = g.C + m * g.ldc + n0;
+            const bool vec = (n0 + 32 <= g.N) && ((((uintptr_t)Crow) & 15) == 0) && g.epi.aux_out == nullptr;
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o;
+                o.x = talos_epilogue_apply(g.epi, __uint_as_float(r[j]), m, n0 + j, g.C, g.ldc);
+                o.y = talos_epilogue_apply(g.epi, __uint_as_float(r[j + 1]), m, n0 + j + 1, g.C, g.ldc);
+                o.z = talos_epilogue_apply(g.epi, __uint_as_float(r[j + 2]), m, n0 + j + 2, g.C, g.ldc);
+                o.w = talos_epilogue_apply(g.epi, __uint_as_float(r[j + 3]), m, n0 + j + 3, g.C, g.ldc);
+                *(float4*)(Crow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < g.N) Crow[j] = talos_epilogue_apply(g.epi, __uint_as_float(r[j]), m, n0 + j, g.C, g.ldc);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty + acc);
+      acc_phase[acc] ^= 1; acc ^= 1;
+    }
+  } else if (X3) {
+    // ------------------------------------------------------------- converter (4 warps): fp32 -> (hi, lo) TF32 pair
+    const int ct = threadIdx.x - 192;                          // 0..127
+    int stage = 0; uint32_t phase = 0; bool ok = true;
+    for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
+      const int ks = it / tiles_mn;
+      const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(full + stage, phase, abort_flag)) { ok = false; break; }
+        // The split is elementwise, so it is oblivious to the swizzle: same offset in, same offset out.
+        float4* ahi = (float4*)(sA + stage * A_BYTES); float4* alo = (float4*)(sAlo + stage * A_BYTES);
+        float4* bhi = (float4*)(sB + stage * B_BYTES); float4* blo = (float4*)(sBlo + stage * B_BYTES);
+#pragma unroll 4
+        for (int i = ct; i < (A_BYTES + B_BYTES) / 16; i += 128) {
+          float4* hi = i < A_BYTES / 16 ? ahi + i : bhi + (i - A_BYTES / 16);
+          float4* lo = i < A_BYTES / 16 ? alo + i : blo + (i - A_BYTES / 16);
+          float4 v = *hi, h, l;
+          h.x = __uint_as_float(cvt_tf32(v.x)); h.y = __uint_as_float(cvt_tf32(v.y));
+          h.z = __uint_as_float(cvt_tf32(v.z)); h.w = __uint_as_float(cvt_tf32(v.w));
+          l.x = __uint_as_float(cvt_tf32(v.x - h.x)); l.y = __uint_as_float(cvt_tf32(v.y - h.y));
+          l.z = __uint_as_float(cvt_tf32(v.z - h.z)); l.w = __uint_as_float(cvt_tf32(v.w - h.w));
+          *hi = h; *lo = l;
+        }
+        fence_proxy_async();                                   // generic-proxy stores -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(conv + stage);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- tail
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up: report it, give copies still in flight time to land, then release TMEM.
+    if (threadIdx.x == 0) atomicExch(g.status, 1000 + (int)blockIdx.x % 1000);
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr; cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// 2-D fp32 tensor map over a row-major [rows][cols] matrix (cols contiguous), box = [box_rows][32 cols].
+bool make_tmap(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool mn_major) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+  cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool X3>
+size_t tc_smem_bytes() {
+  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + (3 * STAGES + 4) * 8 + 16 + 1024;
+}
+
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN>
+void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& g, int grid) {
+  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN>;
+  size_t smem = tc_smem_bytes<BN, STAGES, X3>();
+  TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, X3 ? 320 : 192, smem, ctx->stream>>>(ta, tb, g);
+  talos_launched(ctx, "gemm_tcgen05");
+}
+
+template <int BN, int STAGES, bool X3>
+void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& g, int grid) {
+  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false>(ctx, ta, tb, g, grid);
+  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true>(ctx, ta, tb, g, grid);
+  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false>(ctx, ta, tb, g, grid);
+  else launch_one<BN, STAGES, X3, true, true>(ctx, ta, tb, g, grid);
+}
+
+void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+               int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
+  const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
+  const int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
+  TcArgs g;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
+  g.m_tiles = (int)ceil_div(M, BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
+  int tiles = g.m_tiles * g.n_tiles, splits = 1;
+  if (tiles * 2 <= ctx->sm_count && g.kb_total >= 16) {
+    splits = (int)std::min<int64_t>(ctx->sm_count / tiles, g.kb_total / 8);
+    if (splits < 2) splits = 1;
+  }
+  g.kb_per_split = (int)ceil_div(g.kb_total, splits);
+  // The tensor core truncates when it adds into the fp32 accumulator, a bias that grows with the
+  // length of the accumulation chain (measured ~7e-9 relative per k element).  The fp32-faithful
+  // mode therefore never chains more than 512 k elements in TMEM; longer reductions are split and
+  // the partial sums are added in fp32 (round-to-nearest) by the reduction kernel.
+  if (x3 && g.kb_per_split > 512 / BK) g.kb_per_split = 512 / BK;
+  splits = (int)ceil_div(g.kb_total, g.kb_per_split);
+  g.splits = splits;
+  if (splits > 1) g.partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)splits * M * N);
+
+  CUtensorMap ta, tb;
+  bool ok = a_mn ? make_tmap(&ta, A, K, M, lda, BK, true) : make_tmap(&ta, A, M, K, lda, BM, false);
+  ok = ok && (b_mn ? make_tmap(&tb, B, K, N, ldb, BK, true) : make_tmap(&tb, B, N, K, ldb, bn, false));
+  TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  int grid = std::min(tiles * splits, ctx->sm_count);
+#define TALOS_TC_CASE(BNv, ST, ST3) if (bn == BNv) { if (x3) launch_major<BNv, ST3, true>(ctx, a_mn, b_mn, ta, tb, g, grid); else launch_major<BNv, ST, false>(ctx, a_mn, b_mn, ta, tb, g, grid); }
+  TALOS_TC_CASE(256, 4, 2) else TALOS_TC_CASE(128, 6, 3) else TALOS_TC_CASE(64, 8, 4) else TALOS_TC_CASE(32, 8, 5)
+#undef TALOS_TC_CASE
+  if (splits > 1) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
+}
+
+// Start-up self-check: every operand layout in both modes against the fp32 CUDA-core kernel on a
+// shape with ragged edges.  Any mismatch or device-side timeout disables the tensor-core path for
+// this context (the fp32 kernel then serves all modes) instead of returning wrong numbers.
+bool self_check(talos_ctx* ctx) {
+  const int M = 200, N = 328, K = 296, LD = 336;
+  size_t elems = (size_t)LD * LD;
+  float *A = nullptr, *B = nullptr, *C0 = nullptr, *C1 = nullptr;
+  std::vector<float> h(elems), r0(elems), r1(elems);
+  uint64_t s = 0x243F6A8885A308D3ULL;
+  for (auto& v : h) { s = s * 6364136223846793005ULL + 1442695040888963407ULL; v = (float)((double)(s >> 11) / 9007199254740992.0 * 2.0 - 1.0); }
+  bool pass = true;
+  const bool dbg = getenv("TALOS_DEBUG") != nullptr;
+  try {
+    TALOS_CHECK_CUDA(cudaMalloc(&A, elems * 4)); TALOS_CHECK_CUDA(cudaMalloc(&B, elems * 4));
+    TALOS_CHECK_CUDA(cudaMalloc(&C0, elems * 4)); TALOS_CHECK_CUDA(cudaMalloc(&C1, elems * 4));
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(A, h.data(), elems * 4, cudaMemcpyHostToDevice, ctx->stream));
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(B, h.data() + 17, (elems - 17) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    EpiArgs e{nullptr, nullptr, 0, nullptr, 0, 0, 0, 0};
+    for (int opA = 0; opA < 2 && (pass || dbg); ++opA)
+      for (int opB = 0; opB < 2 && (pass || dbg); ++opB) {
+        TALOS_CHECK_CUDA(cudaMemsetAsync(C0, 0, elems * 4, ctx->stream));
+        talos_gemm_fp32_launch(ctx, opA, opB, M, N, K, A, LD, 0, B, LD, 0, C0, LD, 0, 1, e);
+        TALOS_CHECK_CUDA(cudaMemcpyAsync(r0.data(), C0, elems * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        for (int mode = TALOS_MODE_TF32X3; mode <= TALOS_MODE_TF32 && (pass || dbg); ++mode) {
+          TALOS_CHECK_CUDA(cudaMemsetAsync(C1, 0, elems * 4, ctx->stream));
+          tc_launch(ctx, opA, opB, M, N, K, A, LD, B, LD, C1, LD, mode, e);
+          TALOS_CHECK_CUDA(cudaMemcpyAsync(r1.data(), C1, elems * 4, cudaMemcpyDeviceToHost, ctx->stream));
+          TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+          int32_t st = 0; TALOS_CHECK_CUDA(cudaMemcpy(&st, ctx->dev_status, 4, cudaMemcpyDeviceToHost));
+          if (dbg) fprintf(stderr, "[talos self-check] opA=%d opB=%d mode=%d status=%d\n", opA, opB, mode, st);
+          if (st != 0) { cudaMemset(ctx->dev_status, 0, 64); pass = false; if (!dbg) break; }
+          double num = 0, den = 0;
+          for (int m = 0; m < M; ++m) for (int n = 0; n < N; ++n) { double d = (double)r1[(size_t)m * LD + n] - r0[(size_t)m * LD + n]; num += d * d; den += (double)r0[(size_t)m * LD + n] * r0[(size_t)m * LD + n]; }
+          double rel = sqrt(num / (den > 0 ? den : 1));
+          if (dbg) fprintf(stderr, "[talos self-check]   rel err %.3e  c[0]=%g ref %g c[last]=%g ref %g\n", rel, r1[0], r0[0], r1[(size_t)(M - 1) * LD + N - 1], r0[(size_t)(M - 1) * LD + N - 1]);
+          bool good = rel <= (mode == TALOS_MODE_TF32 ? 2e-3 : 5e-6);
+          if (!good) { pass = false; if (dbg) { good = true; continue; } }
+          for (int m = 0; m < LD && pass; ++m) for (int n = (m < M ? N : 0); n < LD; ++n) if (r1[(size_t)m * LD + n] != 0.f) { pass = false; break; }   // nothing outside [M,N]
+        }
+      }
+  } catch (const talos_error&) { pass = false; cudaGetLastError(); }
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(A); cudaFree(B); cudaFree(C0); cudaFree(C1);
+  return pass;
+}
+
+}  // namespace
+
+bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                          const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
+  if (ctx->tc_state < 0) return false;
+  // TMA needs 16-byte aligned bases and row pitches; tiny problems are launch-bound and stay on CUDA cores.
+  if ((((uintptr_t)A | (uintptr_t)B) & 15) || (lda & 3) || (ldb & 3) || K < 1) return false;
+  if (M * N * K < (1LL << 18) || M < 1 || N < 1) return false;
+  if (getenv("TALOS_DISABLE_TENSOR_CORES")) return false;
+  if (ctx->tc_state == 0) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(ctx->stream, &cap);
+    if (cap != cudaStreamCaptureStatusNone) return false;      // cannot self-check inside a capture
+    ctx->tc_state = self_check(ctx) ? 1 : -1;
+    if (ctx->tc_state < 0) return false;
+  }
+  tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, epi);
+  return true;
+}
+
 void talos_gemm_tc_release(talos_ctx*) {}
