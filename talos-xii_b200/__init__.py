@@ -167,3 +167,114 @@ def torch_context(device=0):
     with the library's kernels (torch is used for device memory and streams only)."""
     import torch
     return Context(device, torch.cuda.current_stream(device).cuda_stream)
+
+
+# ---------------------------------------------------------------------------------------------
+# PPO trainer (include/talos_b200_ppo.h)
+
+
+class PpoConfig(C.Structure):
+    """Mirror of `talos_ppo_config`; defaults are the reference's constants (src/ppo.rs:17-21, :509-511, :567)."""
+    _fields_ = [("obs_dim", C.c_int32), ("hidden", C.c_int32), ("n_actions", C.c_int32), ("minibatch", C.c_int32),
+                ("mode", C.c_int32), ("clip", C.c_float), ("c_value", C.c_float), ("c_entropy", C.c_float), ("lr", C.c_float),
+                ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float)]
+
+    def __init__(self, obs_dim, hidden, n_actions, minibatch, mode=MODE_TF32X3, clip=0.2, c_value=0.5, c_entropy=0.01,
+                 lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8):
+        super().__init__(obs_dim, hidden, n_actions, minibatch, mode, clip, c_value, c_entropy, lr, beta1, beta2, eps)
+
+
+class Comm:
+    """NCCL communicator of one rank (talos_comm).  `unique_id()` on rank 0, ship the bytes, then Comm(ctx, id, n, r)."""
+
+    @staticmethod
+    def unique_id():
+        buf = (C.c_uint8 * 128)()
+        lib.talos_comm_unique_id(buf)
+        return bytes(buf)
+
+    def __init__(self, ctx, uid, nranks, rank):
+        h = C.c_void_p()
+        buf = (C.c_uint8 * 128).from_buffer_copy(uid)
+        lib.talos_comm_init(ctx.handle, buf, nranks, rank, C.byref(h))
+        self.handle, self.ctx, self.nranks, self.rank = h, ctx, nranks, rank
+
+    def allreduce_sum(self, dev_ptr, n):
+        lib.talos_comm_allreduce_sum(self.handle, dev_ptr, n)
+
+    def close(self):
+        if self.handle:
+            lib.talos_comm_destroy(self.handle)
+            self.handle = None
+
+
+class PPOTrainer:
+    """Host mirror of the optimisation half of `PPO` (src/ppo.rs:555-770) for the MLP actor-critic."""
+    NAMES = ["w1", "b1", "w2", "b2", "wp", "bp", "wv", "bv"]
+
+    def __init__(self, ctx, cfg, comm=None):
+        h = C.c_void_p()
+        lib.talos_ppo_create(ctx.handle, C.byref(cfg), C.byref(h))
+        self.handle, self.ctx, self.cfg, self.comm = h, ctx, cfg, comm
+        n = C.c_int64()
+        lib.talos_ppo_param_count(h, C.byref(n))
+        self.n_params = n.value
+
+    def _shapes(self):
+        c = self.cfg
+        return [(c.obs_dim, c.hidden), (c.hidden,), (c.hidden, c.hidden), (c.hidden,), (c.hidden, c.n_actions), (c.n_actions,),
+                (c.hidden, 1), (1,)]
+
+    def set_params(self, params):
+        """`params`: dict name -> array in the canonical order, or one flat fp32 array."""
+        import numpy as np
+        if isinstance(params, dict):
+            flat = np.concatenate([np.asarray(params[k], dtype=np.float32).ravel() for k in self.NAMES])
+        else:
+            flat = np.ascontiguousarray(params, dtype=np.float32)
+        assert flat.size == self.n_params, "parameter count mismatch"
+        lib.talos_ppo_set_params_host(self.handle, ptr(flat))
+
+    def get_params(self):
+        import numpy as np
+        flat = np.empty(self.n_params, dtype=np.float32)
+        lib.talos_ppo_get_params_host(self.handle, ptr(flat))
+        out, o = {}, 0
+        for k, shp in zip(self.NAMES, self._shapes()):
+            n = int(np.prod(shp)); out[k] = flat[o:o + n].reshape(shp); o += n
+        return out
+
+    def reset_optimizer(self):
+        lib.talos_ppo_reset_optimizer(self.handle)
+
+    def forward(self, obs_dev, n, logits_dev=None, values_dev=None):
+        lib.talos_ppo_forward(self.handle, ptr(obs_dev), n, ptr(logits_dev), ptr(values_dev))
+
+    def log_prob(self, obs_dev, actions_dev, n, out_dev):
+        lib.talos_ppo_log_prob(self.handle, ptr(obs_dev), ptr(actions_dev), n, ptr(out_dev))
+
+    def step(self, obs, actions, old_logp, adv, ret, n):
+        lib.talos_ppo_step(self.handle, self.comm.handle if self.comm else None, ptr(obs), ptr(actions), ptr(old_logp), ptr(adv), ptr(ret), n)
+
+    def update(self, obs, actions, old_logp, adv, ret, N, epochs, kl_stop=0.0, host=False):
+        """Runs the epochs x minibatches loops; returns the per-epoch mean approx-KL list.
+        host=True takes HOST arrays (numpy / pinned torch) and copies them inside the call."""
+        kls = (C.c_float * max(1, epochs))(); run = C.c_int32()
+        fn = lib.talos_ppo_update_host if host else lib.talos_ppo_update
+        fn(self.handle, self.comm.handle if self.comm else None, ptr(obs), ptr(actions), ptr(old_logp), ptr(adv), ptr(ret), N, epochs,
+           kl_stop, kls, C.byref(run))
+        return [kls[i] for i in range(run.value)]
+
+    def last_loss(self):
+        v = C.c_float()
+        lib.talos_ppo_last_loss(self.handle, C.byref(v))
+        return v.value
+
+    @property
+    def launches_per_step(self):
+        return lib.talos_ppo_launches_per_step(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib.talos_ppo_destroy(self.handle)
+            self.handle = None

@@ -91,8 +91,13 @@ __global__ void sumsq_stage1_kernel(const float* __restrict__ g, long long n, fl
 // every thread re-sums the (few) block partials in the same order, so the result is deterministic.
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                             long long n, float lr, float b1, float b2, float eps, float inv_bc1, float inv_bc2,
-                            float grad_scale, const float* __restrict__ norm_partial, int nparts, float clip_norm) {
+                            float grad_scale, const float* __restrict__ norm_partial, int nparts, float clip_norm,
+                            const float* __restrict__ count_ptr, float* __restrict__ stats_out) {
   float coef = grad_scale;
+  if (count_ptr) {                       // gradients hold sums over `count` samples (the tail of the flat buffer)
+    coef = grad_scale / fmaxf(count_ptr[0], 1.f);
+    if (stats_out && blockIdx.x == 0 && threadIdx.x < 4) stats_out[threadIdx.x] = count_ptr[(int)threadIdx.x - 2];
+  }
   if (norm_partial) {
     float tot = 0.f;
     for (int i = 0; i < nparts; ++i) tot += norm_partial[i];
@@ -132,14 +137,9 @@ TALOS_API talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logit
   TALOS_ENTRY_END
 }
 
-TALOS_API talos_status talos_adam_step(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
-                                       int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
-                                       float clip_norm) {
-  TALOS_ENTRY_BEGIN
-  talos_check_ctx(ctx);
-  TALOS_REQUIRE(n >= 0 && t >= 1, TALOS_ERR_ARG, "Adam step number must be >= 1");
-  if (n == 0) return TALOS_OK;
-  TALOS_REQUIRE(params && grads && m && v, TALOS_ERR_ARG, "null pointer");
+void talos_adam_launch(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n, int64_t t, float lr,
+                       float beta1, float beta2, float eps, float grad_scale, const float* count_ptr, float clip_norm,
+                       float* stats_out) {
   const double bc1 = 1.0 - pow((double)beta1, (double)t), bc2 = 1.0 - pow((double)beta2, (double)t);
   float* norm_partial = nullptr; int nparts = 0;
   if (clip_norm > 0.f) {
@@ -149,7 +149,19 @@ TALOS_API talos_status talos_adam_step(talos_ctx* ctx, float* params, const floa
     talos_launched(ctx, "adam_sumsq");
   }
   adam_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(params, grads, m, v, n, lr, beta1, beta2, eps, (float)(1.0 / bc1),
-                                                                  (float)(1.0 / bc2), grad_scale, norm_partial, nparts, clip_norm);
+                                                                  (float)(1.0 / bc2), grad_scale, norm_partial, nparts, clip_norm,
+                                                                  count_ptr, stats_out);
   talos_launched(ctx, "adam");
+}
+
+TALOS_API talos_status talos_adam_step(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
+                                       int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
+                                       float clip_norm) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(n >= 0 && t >= 1, TALOS_ERR_ARG, "Adam step number must be >= 1");
+  if (n == 0) return TALOS_OK;
+  TALOS_REQUIRE(params && grads && m && v, TALOS_ERR_ARG, "null pointer");
+  talos_adam_launch(ctx, params, grads, m, v, n, t, lr, beta1, beta2, eps, grad_scale, nullptr, clip_norm, nullptr);
   TALOS_ENTRY_END
 }

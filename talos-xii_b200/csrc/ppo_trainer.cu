@@ -1,0 +1,317 @@
+// Data-parallel PPO actor-critic update: the optimisation loops of PPO::update (src/ppo.rs:680-769)
+// for an MLP actor-critic, one fused sequence of GEMM / loss / Adam launches per minibatch.
+#include <vector>
+
+#include "common.cuh"
+#include "../../include/talos_b200_ppo.h"
+
+// internal launchers of other translation units
+void talos_adam_launch(talos_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, int64_t t, float lr, float b1,
+                       float b2, float eps, float grad_scale, const float* count_ptr, float clip_norm, float* stats_out);
+
+struct talos_ppo {
+  talos_ctx* ctx; talos_ppo_config cfg;
+  int HP;                              // padded width of the fused head [policy | value | 0...]
+  int64_t n_int;                       // floats of the internal flat layout
+  int64_t o_w1, o_b1, o_w2, o_b2, o_wh, o_bh;
+  float *params, *grads, *m, *v;       // grads has 4 extra floats: {sum loss, sum kl, count, unused}
+  float *h1, *h2, *z, *dz, *dh2, *dh1; // activations for one minibatch
+  float* step_stats;                   // [max_steps][4] copy of the tail after each step's exchange
+  int64_t t = 0; int64_t steps_in_epoch = 0; int64_t last_launches = 0;
+  std::vector<float> host_tmp;
+};
+
+namespace {
+
+constexpr int MAX_STEPS_PER_EPOCH = 4096;
+
+void gemm(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+          int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& e) {
+  if (mode != TALOS_MODE_FP32 && talos_gemm_tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, e)) return;
+  talos_gemm_fp32_launch(ctx, opA, opB, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, e);
+}
+
+__global__ void unpack_heads_kernel(const float* __restrict__ z, int HP, int A, long long n, float* __restrict__ logits, float* __restrict__ values) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * (A + 1)) return;
+  long long r = i / (A + 1); int c = (int)(i % (A + 1));
+  float v = z[r * HP + c];
+  if (c < A) { if (logits) logits[r * A + c] = v; } else if (values) values[r] = v;
+}
+__global__ void log_prob_kernel(const float* __restrict__ z, int HP, int A, const int* __restrict__ actions, long long n, float* __restrict__ out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float* l = z + i * HP; float mx = -INFINITY;
+  for (int a = 0; a < A; ++a) mx = fmaxf(mx, l[a]);
+  float se = 0.f; for (int a = 0; a < A; ++a) se += expf(l[a] - mx);
+  out[i] = l[actions[i]] - (logf(se) + mx);
+}
+
+void forward(talos_ppo* p, const float* obs, int64_t n) {
+  const auto& c = p->cfg; talos_ctx* ctx = p->ctx; const float* P = p->params;
+  EpiArgs e1{P + p->o_b1, nullptr, 0, nullptr, 0, TALOS_ACT_TANH, 0, 0};
+  gemm(ctx, 0, 0, n, c.hidden, c.obs_dim, obs, c.obs_dim, P + p->o_w1, c.hidden, p->h1, c.hidden, c.mode, e1);
+  EpiArgs e2{P + p->o_b2, nullptr, 0, nullptr, 0, TALOS_ACT_TANH, 0, 0};
+  gemm(ctx, 0, 0, n, c.hidden, c.hidden, p->h1, c.hidden, P + p->o_w2, c.hidden, p->h2, c.hidden, c.mode, e2);
+  EpiArgs e3{P + p->o_bh, nullptr, 0, nullptr, 0, 0, 0, 0};
+  gemm(ctx, 0, 0, n, p->HP, c.hidden, p->h2, c.hidden, P + p->o_wh, p->HP, p->z, p->HP, c.mode, e3);
+}
+
+void pack_params(talos_ppo* p, const float* canon, float* internal) {
+  const auto& c = p->cfg; const int64_t H = c.hidden, O = c.obs_dim, A = c.n_actions;
+  std::fill(internal, internal + p->n_int, 0.f);
+  const float* s = canon;
+  std::copy(s, s + O * H, internal + p->o_w1); s += O * H;
+  std::copy(s, s + H, internal + p->o_b1); s += H;
+  std::copy(s, s + H * H, internal + p->o_w2); s += H * H;
+  std::copy(s, s + H, internal + p->o_b2); s += H;
+  for (int64_t r = 0; r < H; ++r) for (int64_t a = 0; a < A; ++a) internal[p->o_wh + r * p->HP + a] = s[r * A + a];
+  s += H * A;
+  for (int64_t a = 0; a < A; ++a) internal[p->o_bh + a] = s[a];
+  s += A;
+  for (int64_t r = 0; r < H; ++r) internal[p->o_wh + r * p->HP + A] = s[r];
+  s += H;
+  internal[p->o_bh + A] = s[0];
+}
+void unpack_params(talos_ppo* p, const float* internal, float* canon) {
+  const auto& c = p->cfg; const int64_t H = c.hidden, O = c.obs_dim, A = c.n_actions;
+  float* d = canon;
+  std::copy(internal + p->o_w1, internal + p->o_w1 + O * H, d); d += O * H;
+  std::copy(internal + p->o_b1, internal + p->o_b1 + H, d); d += H;
+  std::copy(internal + p->o_w2, internal + p->o_w2 + H * H, d); d += H * H;
+  std::copy(internal + p->o_b2, internal + p->o_b2 + H, d); d += H;
+  for (int64_t r = 0; r < H; ++r) for (int64_t a = 0; a < A; ++a) d[r * A + a] = internal[p->o_wh + r * p->HP + a];
+  d += H * A;
+  for (int64_t a = 0; a < A; ++a) d[a] = internal[p->o_bh + a];
+  d += A;
+  for (int64_t r = 0; r < H; ++r) d[r] = internal[p->o_wh + r * p->HP + A];
+  d += H;
+  d[0] = internal[p->o_bh + A];
+}
+
+void check(talos_ppo* p) { TALOS_REQUIRE(p != nullptr, TALOS_ERR_ARG, "null trainer"); talos_check_ctx(p->ctx); }
+
+void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions, const float* old_logp, const float* adv,
+          const float* ret, int64_t n) {
+  const auto& c = p->cfg; talos_ctx* ctx = p->ctx; const float* P = p->params; float* G = p->grads;
+  const int64_t H = c.hidden, HP = p->HP;
+  const int64_t l0 = ctx->launches.load();
+  float* tail = G + p->n_int;
+  TALOS_CHECK_CUDA(cudaMemsetAsync(tail, 0, 4 * sizeof(float), ctx->stream));      // Adam::zero_grad (src/ppo.rs:686); GEMMs overwrite the rest
+  forward(p, obs, n);
+  // per-sample loss and its gradient w.r.t. [logits | value]; sums (denominator 1), divided by the global count in Adam
+  talos_status st = talos_ppo_loss_fwd_bwd(ctx, p->z, HP, p->z + c.n_actions, HP, actions, old_logp, adv, ret, n, c.n_actions, c.clip,
+                                           c.c_value, c.c_entropy, 1.0f, p->dz, HP, p->dz + c.n_actions, HP, tail);
+  if (st) throw talos_error(st, talos_last_error_string());
+  EpiArgs none{nullptr, nullptr, 0, nullptr, 0, 0, 0, 0};
+  // heads: dWh = h2^T.dz ; dbh = colsum(dz) ; dh2 = (dz.Wh^T) * (1 - h2^2)
+  gemm(ctx, 1, 0, H, HP, n, p->h2, H, p->dz, HP, G + p->o_wh, HP, c.mode, none);
+  if ((st = talos_colsum(ctx, p->dz, G + p->o_bh, n, HP, 0))) throw talos_error(st, talos_last_error_string());
+  EpiArgs d2{nullptr, nullptr, 0, p->h2, H, 0, TALOS_ACT_TANH, 0};
+  gemm(ctx, 0, 1, n, H, HP, p->dz, HP, P + p->o_wh, HP, p->dh2, H, c.mode, d2);
+  // layer 2
+  gemm(ctx, 1, 0, H, H, n, p->h1, H, p->dh2, H, G + p->o_w2, H, c.mode, none);
+  if ((st = talos_colsum(ctx, p->dh2, G + p->o_b2, n, H, 0))) throw talos_error(st, talos_last_error_string());
+  EpiArgs d1{nullptr, nullptr, 0, p->h1, H, 0, TALOS_ACT_TANH, 0};
+  gemm(ctx, 0, 1, n, H, H, p->dh2, H, P + p->o_w2, H, p->dh1, H, c.mode, d1);
+  // layer 1 (no gradient w.r.t. the observations)
+  gemm(ctx, 1, 0, c.obs_dim, H, n, obs, c.obs_dim, p->dh1, H, G + p->o_w1, H, c.mode, none);
+  if ((st = talos_colsum(ctx, p->dh1, G + p->o_b1, n, H, 0))) throw talos_error(st, talos_last_error_string());
+  if (comm) { if ((st = talos_comm_allreduce_sum(comm, G, p->n_int + 4))) throw talos_error(st, talos_last_error_string()); }
+  p->t += 1;
+  float* stat_slot = p->step_stats + 4 * (p->steps_in_epoch % MAX_STEPS_PER_EPOCH);
+  talos_adam_launch(ctx, p->params, G, p->m, p->v, p->n_int, p->t, c.lr, c.beta1, c.beta2, c.eps, 1.0f, tail + 2, 0.f, stat_slot);
+  p->steps_in_epoch += 1;
+  p->last_launches = ctx->launches.load() - l0;
+}
+
+void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions, const float* old_logp, const float* adv,
+            const float* ret, int64_t N, int32_t epochs, float kl_stop, float* epoch_kl, int32_t* epochs_run) {
+  const int64_t mb = p->cfg.minibatch;
+  int32_t done = 0;
+  std::vector<float> stats;
+  for (int32_t e = 0; e < epochs; ++e) {
+    p->steps_in_epoch = 0;
+    for (int64_t s = 0; s < N; s += mb) {
+      int64_t n = std::min(mb, N - s);
+      step(p, comm, obs + s * p->cfg.obs_dim, actions + s, old_logp + s, adv + s, ret + s, n);
+      TALOS_REQUIRE(p->steps_in_epoch <= MAX_STEPS_PER_EPOCH, TALOS_ERR_UNSUPPORTED, "too many minibatches per epoch");
+    }
+    done = e + 1;
+    // mean approx-KL of the epoch (src/ppo.rs:729-731, :762-767): the step's device->host read
+    stats.resize(4 * (size_t)p->steps_in_epoch);
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(stats.data(), p->step_stats, stats.size() * sizeof(float), cudaMemcpyDeviceToHost, p->ctx->stream));
+    TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+    double kl = 0, cnt = 0;
+    for (int64_t i = 0; i < p->steps_in_epoch; ++i) { kl += stats[4 * i + 1]; cnt += stats[4 * i + 2]; }
+    float mean_kl = cnt > 0 ? (float)(kl / cnt) : 0.f;
+    if (epoch_kl) epoch_kl[e] = mean_kl;
+    if (kl_stop > 0.f && mean_kl > kl_stop * 1.5f) break;
+  }
+  if (epochs_run) *epochs_run = done;
+}
+
+}  // namespace
+
+TALOS_API talos_status talos_ppo_create(talos_ctx* ctx, const talos_ppo_config* cfg, talos_ppo** out) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(cfg && out, TALOS_ERR_ARG, "null pointer");
+  TALOS_REQUIRE(cfg->obs_dim >= 1 && cfg->hidden >= 1 && cfg->n_actions >= 1 && cfg->n_actions <= 63 && cfg->minibatch >= 1,
+                TALOS_ERR_SHAPE, "bad PPO configuration");
+  TALOS_REQUIRE(cfg->mode >= TALOS_MODE_FP32 && cfg->mode <= TALOS_MODE_TF32, TALOS_ERR_ARG, "bad mode");
+  talos_ppo* p = new talos_ppo();
+  p->ctx = ctx; p->cfg = *cfg;
+  const int64_t H = cfg->hidden, O = cfg->obs_dim, mb = cfg->minibatch;
+  p->HP = cfg->n_actions + 1 <= 32 ? 32 : 64;
+  auto up4 = [](int64_t x) { return (x + 3) & ~int64_t(3); };     // keep every matrix 16-byte aligned for TMA
+  int64_t o = 0;
+  p->o_w1 = o; o = up4(o + O * H); p->o_b1 = o; o = up4(o + H); p->o_w2 = o; o = up4(o + H * H); p->o_b2 = o; o = up4(o + H);
+  p->o_wh = o; o = up4(o + H * p->HP); p->o_bh = o; o = up4(o + p->HP);
+  p->n_int = o;
+  auto alloc = [&](float** ptr, int64_t n) {
+    cudaError_t e = cudaMalloc(ptr, sizeof(float) * (size_t)n);
+    if (e != cudaSuccess) { cudaGetLastError(); throw talos_error(TALOS_ERR_ALLOC, "PPO buffer allocation failed"); }
+    TALOS_CHECK_CUDA(cudaMemsetAsync(*ptr, 0, sizeof(float) * (size_t)n, ctx->stream));
+  };
+  alloc(&p->params, p->n_int); alloc(&p->grads, p->n_int + 4); alloc(&p->m, p->n_int); alloc(&p->v, p->n_int);
+  alloc(&p->h1, mb * H); alloc(&p->h2, mb * H); alloc(&p->dh1, mb * H); alloc(&p->dh2, mb * H);
+  alloc(&p->z, mb * p->HP); alloc(&p->dz, mb * p->HP);
+  alloc(&p->step_stats, 4 * MAX_STEPS_PER_EPOCH);
+  *out = p;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_destroy(talos_ppo* p) {
+  TALOS_ENTRY_BEGIN
+  if (!p) return TALOS_OK;
+  cudaSetDevice(p->ctx->device); cudaStreamSynchronize(p->ctx->stream);
+  for (float* q : {p->params, p->grads, p->m, p->v, p->h1, p->h2, p->dh1, p->dh2, p->z, p->dz, p->step_stats}) cudaFree(q);
+  delete p;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_param_count(talos_ppo* p, int64_t* n_out) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(p && n_out, TALOS_ERR_ARG, "null pointer");
+  const auto& c = p->cfg;
+  *n_out = (int64_t)c.obs_dim * c.hidden + c.hidden + (int64_t)c.hidden * c.hidden + c.hidden + (int64_t)c.hidden * c.n_actions +
+           c.n_actions + c.hidden + 1;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_set_params_host(talos_ppo* p, const float* flat) {
+  TALOS_ENTRY_BEGIN
+  check(p); TALOS_REQUIRE(flat != nullptr, TALOS_ERR_ARG, "null pointer");
+  p->host_tmp.resize((size_t)p->n_int);
+  pack_params(p, flat, p->host_tmp.data());
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(p->params, p->host_tmp.data(), sizeof(float) * (size_t)p->n_int, cudaMemcpyHostToDevice, p->ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ppo_get_params_host(talos_ppo* p, float* flat) {
+  TALOS_ENTRY_BEGIN
+  check(p); TALOS_REQUIRE(flat != nullptr, TALOS_ERR_ARG, "null pointer");
+  p->host_tmp.resize((size_t)p->n_int);
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(p->host_tmp.data(), p->params, sizeof(float) * (size_t)p->n_int, cudaMemcpyDeviceToHost, p->ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  unpack_params(p, p->host_tmp.data(), flat);
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ppo_reset_optimizer(talos_ppo* p) {
+  TALOS_ENTRY_BEGIN
+  check(p);
+  TALOS_CHECK_CUDA(cudaMemsetAsync(p->m, 0, sizeof(float) * (size_t)p->n_int, p->ctx->stream));
+  TALOS_CHECK_CUDA(cudaMemsetAsync(p->v, 0, sizeof(float) * (size_t)p->n_int, p->ctx->stream));
+  p->t = 0;
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ppo_set_lr(talos_ppo* p, float lr) {
+  TALOS_ENTRY_BEGIN
+  TALOS_REQUIRE(p != nullptr, TALOS_ERR_ARG, "null trainer"); p->cfg.lr = lr;
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_forward(talos_ppo* p, const float* obs, int64_t n, float* logits_out, float* values_out) {
+  TALOS_ENTRY_BEGIN
+  check(p); TALOS_REQUIRE(n >= 0 && (obs || n == 0), TALOS_ERR_ARG, "bad observations");
+  const auto& c = p->cfg;
+  for (int64_t s = 0; s < n; s += c.minibatch) {
+    int64_t m = std::min<int64_t>(c.minibatch, n - s);
+    forward(p, obs + s * c.obs_dim, m);
+    int64_t total = m * (c.n_actions + 1);
+    unpack_heads_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, p->ctx->stream>>>(p->z, p->HP, c.n_actions, m, logits_out ? logits_out + s * c.n_actions : nullptr,
+                                                                                     values_out ? values_out + s : nullptr);
+    talos_launched(p->ctx, "unpack_heads");
+  }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ppo_log_prob(talos_ppo* p, const float* obs, const int32_t* actions, int64_t n, float* out) {
+  TALOS_ENTRY_BEGIN
+  check(p); TALOS_REQUIRE(n >= 0 && ((obs && actions && out) || n == 0), TALOS_ERR_ARG, "null pointer");
+  const auto& c = p->cfg;
+  for (int64_t s = 0; s < n; s += c.minibatch) {
+    int64_t m = std::min<int64_t>(c.minibatch, n - s);
+    forward(p, obs + s * c.obs_dim, m);
+    log_prob_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, p->ctx->stream>>>(p->z, p->HP, c.n_actions, actions + s, m, out + s);
+    talos_launched(p->ctx, "log_prob");
+  }
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions,
+                                      const float* old_logp, const float* adv, const float* ret, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  check(p);
+  TALOS_REQUIRE(n >= 1 && n <= p->cfg.minibatch, TALOS_ERR_SHAPE, "minibatch larger than configured");
+  TALOS_REQUIRE(obs && actions && old_logp && adv && ret, TALOS_ERR_ARG, "null pointer");
+  step(p, comm, obs, actions, old_logp, adv, ret, n);
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions,
+                                        const float* old_logp, const float* adv, const float* ret, int64_t N, int32_t epochs,
+                                        float kl_stop, float* epoch_kl_host, int32_t* epochs_run_out) {
+  TALOS_ENTRY_BEGIN
+  check(p);
+  TALOS_REQUIRE(N >= 0 && epochs >= 0, TALOS_ERR_SHAPE, "bad update size");
+  if (N == 0) { if (epochs_run_out) *epochs_run_out = 0; return TALOS_OK; }     // empty memory: nothing to do (src/ppo.rs:626-628)
+  TALOS_REQUIRE(obs && actions && old_logp && adv && ret, TALOS_ERR_ARG, "null pointer");
+  update(p, comm, obs, actions, old_logp, adv, ret, N, epochs, kl_stop, epoch_kl_host, epochs_run_out);
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_update_host(talos_ppo* p, talos_comm* comm, const float* obs_h, const int32_t* actions_h,
+                                             const float* old_logp_h, const float* adv_h, const float* ret_h, int64_t N,
+                                             int32_t epochs, float kl_stop, float* epoch_kl_host, int32_t* epochs_run_out) {
+  TALOS_ENTRY_BEGIN
+  check(p);
+  TALOS_REQUIRE(N >= 0 && epochs >= 0, TALOS_ERR_SHAPE, "bad update size");
+  if (N == 0) { if (epochs_run_out) *epochs_run_out = 0; return TALOS_OK; }
+  TALOS_REQUIRE(obs_h && actions_h && old_logp_h && adv_h && ret_h, TALOS_ERR_ARG, "null pointer");
+  const int64_t O = p->cfg.obs_dim;
+  size_t bytes = sizeof(float) * (size_t)(N * O) + 4 * sizeof(float) * (size_t)N + 1024;
+  char* base = (char*)talos_workspace2(p->ctx, bytes);
+  float* obs = (float*)base; int32_t* actions = (int32_t*)(obs + N * O);
+  float* old_logp = (float*)(actions + N); float* adv = old_logp + N; float* ret = adv + N;
+  cudaStream_t s = p->ctx->stream;
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(obs, obs_h, sizeof(float) * (size_t)(N * O), cudaMemcpyHostToDevice, s));
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(actions, actions_h, sizeof(int32_t) * (size_t)N, cudaMemcpyHostToDevice, s));
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(old_logp, old_logp_h, sizeof(float) * (size_t)N, cudaMemcpyHostToDevice, s));
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(adv, adv_h, sizeof(float) * (size_t)N, cudaMemcpyHostToDevice, s));
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(ret, ret_h, sizeof(float) * (size_t)N, cudaMemcpyHostToDevice, s));
+  update(p, comm, obs, actions, old_logp, adv, ret, N, epochs, kl_stop, epoch_kl_host, epochs_run_out);
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_ppo_last_loss(talos_ppo* p, float* loss_out) {
+  TALOS_ENTRY_BEGIN
+  check(p); TALOS_REQUIRE(loss_out != nullptr, TALOS_ERR_ARG, "null pointer");
+  TALOS_REQUIRE(p->steps_in_epoch > 0, TALOS_ERR_ARG, "no optimizer step has run");
+  float s[4];
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(s, p->step_stats + 4 * ((p->steps_in_epoch - 1) % MAX_STEPS_PER_EPOCH), sizeof(s), cudaMemcpyDeviceToHost, p->ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  *loss_out = s[2] > 0 ? s[0] / s[2] : 0.f;
+  TALOS_ENTRY_END
+}
+TALOS_API int64_t talos_ppo_launches_per_step(talos_ppo* p) { return p ? p->last_launches : 0; }

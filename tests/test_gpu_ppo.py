@@ -1,0 +1,131 @@
+"""GPU parity of the PPO actor-critic update (C ABI trainer) against the oracle's restatement of
+PPO::update's optimisation loops."""
+import numpy as np
+import pytest
+
+import oracle as orc
+from oracle import model as om
+from gpu_util import TOL, dev, host, normal, rel_err, xavier
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx(talos):
+    c = talos.torch_context(0)
+    yield c
+    c.synchronize()
+
+
+def make_problem(N, obs_dim, hidden, A, seed=30):
+    obs = normal(seed, (N, obs_dim)); actions = orc.rng_bounded(seed + 1, N, A)
+    adv = normal(seed + 2, (N,)); ret = normal(seed + 3, (N,))
+    params = dict(w1=xavier(seed + 4, obs_dim, hidden), b1=np.zeros(hidden), w2=xavier(seed + 5, hidden, hidden), b2=np.zeros(hidden),
+                  wp=xavier(seed + 6, hidden, A), bp=np.zeros(A), wv=xavier(seed + 7, hidden, 1), bv=np.zeros(1))
+    return obs, actions, adv, ret, params
+
+
+def run_case(talos, ctx, N, obs_dim, hidden, A, mb, epochs, mode, lr=3e-4, kl_stop=0.0, via_host=False):
+    import torch
+    obs, actions, adv, ret, params = make_problem(N, obs_dim, hidden, A)
+    cfg = talos.PpoConfig(obs_dim, hidden, A, mb, mode, lr=lr)
+    tr = talos.PPOTrainer(ctx, cfg)
+    tr.set_params(params)
+    back = tr.get_params()
+    for k in params:
+        assert np.array_equal(back[k], params[k].astype(np.float32).reshape(back[k].shape)), k   # pack/unpack round trip
+    d_obs, d_act = dev(obs), dev(actions)
+    d_old = torch.empty(N, device="cuda:0")
+    tr.log_prob(d_obs, d_act, N, d_old)              # what the rollout stored (src/ppo.rs:346)
+    ctx.synchronize()
+    model = om.MlpActorCritic(params)
+    ref_old = model.log_prob(obs, actions)
+    assert rel_err(d_old, ref_old) <= TOL[mode]
+    old = orc.f32r(host(d_old))                      # both sides continue from the same stored values
+    lr64 = np.float64(np.float32(lr))
+    ref_kls, _ = om.ppo_update(model, obs, actions, old, adv, ret, epochs, mb, lr=lr64, kl_stop=kl_stop or None)
+    if via_host:
+        kls = tr.update(obs.astype(np.float32), actions, old.astype(np.float32), adv.astype(np.float32), ret.astype(np.float32), N, epochs, kl_stop, host=True)
+    else:
+        kls = tr.update(d_obs, d_act, dev(old), dev(adv), dev(ret), N, epochs, kl_stop)
+    got = tr.get_params()
+    loss = tr.last_loss()
+    tr.close()
+    return got, model.p, kls, ref_kls, params, loss
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_ppo_update_matches_oracle_config5_shape(talos, ctx, mode):
+    # BASELINE config 5 at reduced length: obs 64, trunk 64->256->256 tanh, 16 actions, 4 epochs of consecutive minibatches
+    N, mb, epochs = 16384, 4096, 4
+    got, ref, kls, ref_kls, init, loss = run_case(talos, ctx, N, 64, 256, 16, mb, epochs, mode)
+    tol = TOL[mode]
+    for k in ref:
+        # weights agree to the mode's tolerance; biases start at zero, so they ARE the learned update and are
+        # held to the (looser, lr-sized) bound every update is held to
+        if k.startswith("w"):
+            assert rel_err(got[k], ref[k]) <= tol, (k, rel_err(got[k], ref[k]))
+        delta_ref = ref[k] - init[k]
+        err = rel_err(got[k].astype(np.float64) - init[k].reshape(got[k].shape), delta_ref)
+        assert err <= (5e-3 if mode != 2 else 2e-2), (k, err)
+    assert len(kls) == len(ref_kls) == epochs
+    assert np.allclose(kls, ref_kls, rtol=1e-3 if mode != 2 else 0.1, atol=1e-7)
+    assert np.isfinite(loss)
+
+
+def test_ppo_small_reference_sized_policy(talos, ctx):
+    # the reference's own sizes: 8 observations, 5 actions (src/neural.rs:3, src/ppo.rs:15); ragged last minibatch
+    got, ref, kls, ref_kls, _, _ = run_case(talos, ctx, 1000, 8, 64, 5, 256, 3, 0, lr=1e-3)
+    for k in ref:
+        assert rel_err(got[k], ref[k]) <= 1e-5, k
+    assert np.allclose(kls, ref_kls, rtol=1e-3, atol=1e-8)
+
+
+def test_ppo_update_from_host_buffers_and_kl_early_stop(talos, ctx):
+    got, ref, kls, ref_kls, _, _ = run_case(talos, ctx, 4096, 64, 256, 16, 1024, 6, 1, lr=3e-2, kl_stop=0.015, via_host=True)
+    assert len(kls) == len(ref_kls) and len(kls) < 6          # stops once mean approx-KL > 0.0225 (src/ppo.rs:762-767)
+    for k in ref:
+        assert rel_err(got[k], ref[k]) <= 5e-4, k               # lr 100x larger than the default
+
+
+def test_ppo_forward_argmax_and_empty_update(talos, ctx):
+    import torch
+    N = 8192
+    obs, actions, adv, ret, params = make_problem(N, 64, 256, 16, seed=50)
+    model = om.MlpActorCritic(params)
+    _, _, ref_logits, ref_values = model.forward(obs)
+    top2 = np.sort(ref_logits, axis=1)[:, -2:]; gap = top2[:, 1] - top2[:, 0]
+    for mode in (0, 1, 2):
+        tr = talos.PPOTrainer(ctx, talos.PpoConfig(64, 256, 16, 4096, mode)); tr.set_params(params)
+        lg = torch.empty(N, 16, device="cuda:0"); vl = torch.empty(N, device="cuda:0")
+        tr.forward(dev(obs), N, lg, vl); ctx.synchronize()
+        assert rel_err(lg, ref_logits) <= TOL[mode] and rel_err(vl, ref_values) <= TOL[mode]
+        safe = gap > (1e-5 if mode != 2 else 5e-3)            # identical argmax actions; near-ties are exempt
+        assert np.array_equal(host(lg).argmax(1)[safe], ref_logits.argmax(1)[safe]) and safe.mean() > 0.95
+        assert tr.update(None, None, None, None, None, 0, 4) == []   # empty memory (src/ppo.rs:626-628)
+        tr.close()
+
+
+def test_ppo_minibatch_split_invariance(talos, ctx):
+    # gradients are sums divided by the global count: two ranks x n samples == one rank x 2n samples.
+    # Emulated on one GPU by comparing one step on 2n samples with the averaged sum-gradients the
+    # oracle computes for the two halves.
+    N = 2048
+    obs, actions, adv, ret, params = make_problem(N, 64, 256, 16, seed=70)
+    model = om.MlpActorCritic(params); old = model.log_prob(obs, actions)
+    g_full, _, _ = model.grads(obs, actions, old, adv, ret)
+    acc = None
+    for s in (0, N // 2):
+        g, _, _ = model.grads(obs[s:s + N // 2], actions[s:s + N // 2], old[s:s + N // 2], adv[s:s + N // 2], ret[s:s + N // 2], denom=N)
+        acc = g if acc is None else {k: acc[k] + g[k] for k in g}
+    for k in g_full:
+        assert np.allclose(acc[k], g_full[k], atol=1e-12)
+    tr = talos.PPOTrainer(ctx, talos.PpoConfig(64, 256, 16, N, 0)); tr.set_params(params)
+    tr.step(dev(obs), dev(actions), dev(orc.f32r(old)), dev(adv), dev(ret), N)
+    got = tr.get_params()
+    om.adam_step([model.p[k] for k in model.NAMES], [g_full[k] for k in model.NAMES], [np.zeros_like(model.p[k]) for k in model.NAMES],
+                 [np.zeros_like(model.p[k]) for k in model.NAMES], 1, np.float64(np.float32(3e-4)))
+    for k in model.NAMES:
+        assert rel_err(got[k], model.p[k]) <= 1e-6, k
+    assert tr.launches_per_step > 0
+    tr.close()
