@@ -77,10 +77,19 @@ inline void talos_launched(talos_ctx* ctx, const char* what) {
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // ---- activation helpers shared by the GEMM epilogues and the elementwise kernels ----
+// Branch-free tanh with |abs error| < 2e-7: x - x^3/3 + 2x^5/15 below 0.06 (no cancellation there),
+// 1 - 2/(e^{2|x|}+1) elsewhere with the hardware exp2 / reciprocal approximations.
+__device__ __forceinline__ float talos_tanh(float x) {
+  const float ax = fabsf(x), x2 = x * x;
+  const float poly = x * (1.f + x2 * (-0.33333334f + x2 * 0.13333334f));
+  const float e = __expf(2.f * ax);
+  const float t = copysignf(1.f - __fdividef(2.f, e + 1.f), x);
+  return ax < 0.06f ? poly : t;
+}
 __device__ __forceinline__ float talos_act(float v, int act) {
   switch (act) {
     case TALOS_ACT_RELU: return v > 0.f ? v : 0.f;
-    case TALOS_ACT_TANH: return tanhf(v);
+    case TALOS_ACT_TANH: return talos_tanh(v);
     case TALOS_ACT_SILU: return v / (1.f + __expf(-v));
     default: return v;
   }

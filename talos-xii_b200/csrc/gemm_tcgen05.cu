@@ -69,6 +69,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N_PENDING>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N_PENDING) : "memory"); }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -121,6 +128,55 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+
+// Epilogue over one transposed 32x32 staging tile: lane = column, loop over rows.  The activation
+// and derivative kinds are template parameters so the row loop carries no per-element branches.
+template <int ACT, int DACT>
+__device__ __forceinline__ void epilogue_rows_t(const EpiArgs& e, const float* stage, int lane, long long m0, int rows_valid,
+                                                long long n, bool col_ok, float* C, long long ldc) {
+  const float bias_v = (e.bias && col_ok) ? __ldg(e.bias + n) : 0.f;
+#pragma unroll 4
+  for (int rr = 0; rr < rows_valid; ++rr) {
+    if (!col_ok) continue;
+    const long long m = m0 + rr;
+    float v = stage[rr * 32 + (lane ^ rr)] + bias_v;
+    if (e.aux_out) e.aux_out[m * e.ld_aux_out + n] = v;
+    if (ACT) v = talos_act(v, ACT);
+    if (DACT) v *= talos_dact(__ldg(e.aux_in + m * e.ld_aux_in + n), DACT);
+    if (e.beta) v += C[m * ldc + n];
+    C[m * ldc + n] = v;
+  }
+}
+__device__ __noinline__ void epilogue_rows(const EpiArgs& e, const float* stage, int lane, long long m0, int rows_valid, long long n,
+                                           bool col_ok, float* C, long long ldc) {
+  const int dact = e.aux_in ? e.dact : 0;
+  switch (e.act * 4 + dact) {
+#define TALOS_EPI_CASE(A, D) case (A) * 4 + (D): epilogue_rows_t<A, D>(e, stage, lane, m0, rows_valid, n, col_ok, C, ldc); break;
+    TALOS_EPI_CASE(0, 0) TALOS_EPI_CASE(0, 1) TALOS_EPI_CASE(0, 2) TALOS_EPI_CASE(0, 3)
+    TALOS_EPI_CASE(1, 0) TALOS_EPI_CASE(1, 1) TALOS_EPI_CASE(1, 2) TALOS_EPI_CASE(1, 3)
+    TALOS_EPI_CASE(2, 0) TALOS_EPI_CASE(2, 1) TALOS_EPI_CASE(2, 2) TALOS_EPI_CASE(2, 3)
+    TALOS_EPI_CASE(3, 0) TALOS_EPI_CASE(3, 1) TALOS_EPI_CASE(3, 2) TALOS_EPI_CASE(3, 3)
+#undef TALOS_EPI_CASE
+    default: break;
+  }
+}
+
+// Fused epilogue on one group of four consecutive columns of one accumulator row.  Everything is a
+// named scalar or a float4 (no arrays), so the accumulator values never leave registers.  The host
+// guarantees 16-byte alignment of every operand on this path.
+template <int ACT, int DACT>
+__device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restrict__ bias, const float* __restrict__ aux_in,
+                                                 const float* __restrict__ c_old) {
+  if (bias) { const float4 b = __ldg((const float4*)bias); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+  if (ACT) { v.x = talos_act(v.x, ACT); v.y = talos_act(v.y, ACT); v.z = talos_act(v.z, ACT); v.w = talos_act(v.w, ACT); }
+  if (DACT) {
+    const float4 a = __ldg((const float4*)aux_in);
+    v.x *= talos_dact(a.x, DACT); v.y *= talos_dact(a.y, DACT); v.z *= talos_dact(a.z, DACT); v.w *= talos_dact(a.w, DACT);
+  }
+  if (c_old) { const float4 o = *(const float4*)c_old; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+  return v;
+}
+
 struct TcArgs {
   int M, N, K;
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
@@ -128,13 +184,15 @@ struct TcArgs {
   float* partial;                          // [splits][M][N] when splits > 1
   EpiArgs epi;
   int32_t* status;
+  int tma_out;                             // 1: results leave through TMA stores (tmap_c), 0: direct stores
 };
 
 // Shared storage layout (dynamic, 1024-byte aligned):
 //   [STAGES][A tile (hi)] [STAGES][B tile (hi)] ([STAGES][A lo] [STAGES][B lo] in X3 mode) barriers...
 template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(X3 ? 320 : 192, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcArgs g) {
+__global__ void __launch_bounds__(X3 ? 448 : 320, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_c, TcArgs g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
   extern __shared__ uint8_t smem_raw[];
@@ -143,7 +201,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* sB = sA + STAGES * A_BYTES;
   uint8_t* sAlo = sB + STAGES * B_BYTES;
   uint8_t* sBlo = sAlo + (X3 ? STAGES * A_BYTES : 0);
-  uint64_t* bars = (uint64_t*)(sBlo + (X3 ? STAGES * B_BYTES : 0));
+  float* stage_all = (float*)(sBlo + (X3 ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
+  uint64_t* bars = (uint64_t*)(stage_all + 8 * 32 * 32);
   uint64_t* full = bars;                   // TMA -> (converter | issuer)
   uint64_t* conv = full + STAGES;          // converter -> issuer (X3)
   uint64_t* empty = conv + STAGES;         // issuer (commit) -> TMA
@@ -155,7 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, 4); mbar_init(empty + s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 8); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -229,52 +288,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         acc_phase[acc] ^= 1; acc ^= 1;
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------- epilogue (4 warps, one TMEM lane quadrant each)
-    const int quad = warp & 3;
-    int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
+  } else if (warp < 10) {
+    // ------------------------------------------------------------- epilogue: 8 warps, two per TMEM lane quadrant, each
+    // taking half of the tile's columns.  The epilogue is latency-bound per warp, so it needs the extra warps.
+    const int quad = warp & 3, half = (warp - 2) >> 2;
+    int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
       if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const long long m = (long long)mb * BM + quad * 32 + lane;
+      // Each warp drains its 32-lane quadrant (one accumulator row per lane) 32 columns at a time.
+      const long long m0 = (long long)mb * BM + quad * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-      const bool row_ok = m < g.M;
+      const int rows_valid = (int)min((long long)32, (long long)g.M - m0);
+      float* stage = stage_all + (warp - 2) * (32 * 32);     // one 4 KB buffer per warp
+      constexpr int HALF_COLS = BN >= 64 ? BN / 2 : BN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 32) {
         const long long n0 = (long long)nb * BN + c0;
-        if (n0 >= g.N) break;                                  // uniform across the warp
+        if (n0 >= g.N || rows_valid <= 0) break;               // uniform across the warp
         uint32_t r[32];
         tmem_ld32(t_row + (uint32_t)c0, r);
         tmem_ld_wait();
-        if (row_ok) {
-          if (g.splits > 1) {
-            float* P = g.partial + ((long long)ks * g.M + m) * g.N + n0;
-            const bool vec = (n0 + 32 <= g.N) && ((((uintptr_t)P) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *(float4*)(P + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
-              for (int j = 0; j < 32; ++j) if (n0 + j < g.N) P[j] = __uint_as_float(r[j]);
+        if (g.tma_out) {
+          // Fused epilogue in registers, then a 128B-swizzled 32x32 tile in shared memory that one
+          // lane hands to the TMA store engine (clipped to [M,N] by the tensor map).
+          float* buf = stage;
+          if (store_count >= 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+          {
+            const bool fuse = (g.splits == 1) && (lane < rows_valid);
+            const long long m = m0 + lane;
+            const int dact = g.epi.aux_in ? g.epi.dact : 0;
+            const float* bias_p = (fuse && g.epi.bias) ? g.epi.bias + n0 : nullptr;
+            const float* aux_p = (fuse && dact) ? g.epi.aux_in + m * g.epi.ld_aux_in + n0 : nullptr;
+            const float* cold_p = (fuse && g.epi.beta) ? g.C + m * g.ldc + n0 : nullptr;
+            const int groups = (int)min((long long)8, (g.N - n0) >> 2);     // N is a multiple of 4 on this path
+#define TALOS_EPI_STORE(A, D)                                                                                           \
+  _Pragma("unroll") for (int c = 0; c < 8; ++c) {                                                                      \
+    float4 v = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),    \
+                           __uint_as_float(r[4 * c + 3]));                                                             \
+    if (fuse && c < groups)                                                                                             \
+      v = epilogue_group<A, D>(v, bias_p ? bias_p + 4 * c : nullptr, aux_p ? aux_p + 4 * c : nullptr,                  \
+                               cold_p ? cold_p + 4 * c : nullptr);                                                      \
+    *(float4*)(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) = v;                                                          \
+  }
+            switch (fuse ? g.epi.act * 4 + dact : 0) {
+              case 1: TALOS_EPI_STORE(0, 1) break;
+              case 2: TALOS_EPI_STORE(0, 2) break;
+              case 3: TALOS_EPI_STORE(0, 3) break;
+              case 4: TALOS_EPI_STORE(1, 0) break;
+              case 8: TALOS_EPI_STORE(2, 0) break;
+              case 12: TALOS_EPI_STORE(3, 0) break;
+              default: TALOS_EPI_STORE(0, 0) break;
             }
-          } else {
-            float* Crow = g.C + m * g.ldc + n0;
-            const bool vec = (n0 + 32 <= g.N) && ((((uintptr_t)Crow) & 15) == 0) && g.epi.aux_out == nullptr;
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o;
-                o.x = talos_epilogue_apply(g.epi, __uint_as_float(r[j]), m, n0 + j, g.C, g.ldc);
-                o.y = talos_epilogue_apply(g.epi, __uint_as_float(r[j + 1]), m, n0 + j + 1, g.C, g.ldc);
-                o.z = talos_epilogue_apply(g.epi, __uint_as_float(r[j + 2]), m, n0 + j + 2, g.C, g.ldc);
-                o.w = talos_epilogue_apply(g.epi, __uint_as_float(r[j + 3]), m, n0 + j + 3, g.C, g.ldc);
-                *(float4*)(Crow + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (n0 + j < g.N) Crow[j] = talos_epilogue_apply(g.epi, __uint_as_float(r[j]), m, n0 + j, g.C, g.ldc);
-            }
+#undef TALOS_EPI_STORE
           }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) { tma_store_3d(&tmap_c, buf, (int)n0, (int)m0, ks); tma_store_commit(); }
+          ++store_count;
+        } else {
+          // Unaligned output: transpose through a padded tile so lanes run along the contiguous axis.
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage[lane * 32 + (j ^ lane)] = __uint_as_float(r[j]);    // XOR-swizzled transpose tile
+          __syncwarp();
+          const long long n = n0 + lane;
+          const bool col_ok = n < g.N;
+          if (g.splits > 1) {
+            float* P = g.partial + ((long long)ks * g.M + m0) * g.N + n;
+#pragma unroll 4
+            for (int rr = 0; rr < rows_valid; ++rr) if (col_ok) P[(long long)rr * g.N] = stage[rr * 32 + (lane ^ rr)];
+          } else {
+            epilogue_rows(g.epi, stage, lane, m0, rows_valid, n, col_ok, g.C, g.ldc);
+          }
+          __syncwarp();
         }
       }
       tc_fence_before();
@@ -282,9 +369,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (lane == 0) mbar_arrive(tempty + acc);
       acc_phase[acc] ^= 1; acc ^= 1;
     }
+    if (lane == 0) tma_store_wait_read<0>();                 // shared memory must outlive the stores that read it
+    __syncwarp();
   } else if (X3) {
     // ------------------------------------------------------------- converter (4 warps): fp32 -> (hi, lo) TF32 pair
-    const int ct = threadIdx.x - 192;                          // 0..127
+    const int ct = threadIdx.x - 320;                          // 0..127
     int stage = 0; uint32_t phase = 0; bool ok = true;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int ks = it / tiles_mn;
@@ -355,26 +444,40 @@ bool make_tmap(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, 
   return r == CUDA_SUCCESS;
 }
 
+// 3-D fp32 tensor map for results: [slabs][rows][cols], box = [1][32][32], 128B swizzle.  C itself is one
+// slab; split-K partial sums are `splits` dense slabs, clipped per slab by the map.
+bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)slabs};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)ld * (cuuint64_t)rows * sizeof(float)};
+  cuuint32_t box[3] = {32u, 32u, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 template <int BN, int STAGES, bool X3>
 size_t tc_smem_bytes() {
-  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + (3 * STAGES + 4) * 8 + 16 + 1024;
+  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + 8 * 32 * 32 * 4 + (3 * STAGES + 4) * 8 + 16 + 1024;
 }
 
 template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN>
-void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& g, int grid) {
+void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcArgs& g, int grid) {
   auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN>;
   size_t smem = tc_smem_bytes<BN, STAGES, X3>();
   TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, X3 ? 320 : 192, smem, ctx->stream>>>(ta, tb, g);
+  kern<<<grid, X3 ? 448 : 320, smem, ctx->stream>>>(ta, tb, tc, g);
   talos_launched(ctx, "gemm_tcgen05");
 }
 
 template <int BN, int STAGES, bool X3>
-void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TcArgs& g, int grid) {
-  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false>(ctx, ta, tb, g, grid);
-  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true>(ctx, ta, tb, g, grid);
-  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false>(ctx, ta, tb, g, grid);
-  else launch_one<BN, STAGES, X3, true, true>(ctx, ta, tb, g, grid);
+void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcArgs& g, int grid) {
+  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false>(ctx, ta, tb, tc, g, grid);
+  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true>(ctx, ta, tb, tc, g, grid);
+  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false>(ctx, ta, tb, tc, g, grid);
+  else launch_one<BN, STAGES, X3, true, true>(ctx, ta, tb, tc, g, grid);
 }
 
 void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
@@ -402,10 +505,19 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   CUtensorMap ta, tb;
   bool ok = a_mn ? make_tmap(&ta, A, K, M, lda, BK, true) : make_tmap(&ta, A, M, K, lda, BM, false);
   ok = ok && (b_mn ? make_tmap(&tb, B, K, N, ldb, BK, true) : make_tmap(&tb, B, N, K, ldb, bn, false));
+  // Results leave through TMA stores when the destination is 16-byte aligned with a 16-byte pitch, N is a
+  // multiple of 4 (a TMA store clips the innermost axis in 16-byte units, so a ragged N would spill into the
+  // pitch padding) and the epilogue does not also save the pre-activation; otherwise through direct stores.
+  CUtensorMap tc = ta;
+  g.tma_out = 0;
+  const bool both = epi.act != 0 && epi.aux_in != nullptr && epi.dact != 0;
+  const bool epi_aligned = !(((uintptr_t)epi.bias) & 15) && !(((uintptr_t)epi.aux_in) & 15) && !(epi.ld_aux_in & 3);
+  if (splits > 1) { if (!(N & 3)) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, g.partial, splits, M, N, N); } }
+  else if (!(((uintptr_t)C) & 15) && !(ldc & 3) && !(N & 3) && !epi.aux_out && !both && epi_aligned) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, C, 1, M, N, ldc); }
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   int grid = std::min(tiles * splits, ctx->sm_count);
-#define TALOS_TC_CASE(BNv, ST, ST3) if (bn == BNv) { if (x3) launch_major<BNv, ST3, true>(ctx, a_mn, b_mn, ta, tb, g, grid); else launch_major<BNv, ST, false>(ctx, a_mn, b_mn, ta, tb, g, grid); }
-  TALOS_TC_CASE(256, 4, 2) else TALOS_TC_CASE(128, 6, 3) else TALOS_TC_CASE(64, 8, 4) else TALOS_TC_CASE(32, 8, 5)
+#define TALOS_TC_CASE(BNv, ST, ST3) if (bn == BNv) { if (x3) launch_major<BNv, ST3, true>(ctx, a_mn, b_mn, ta, tb, tc, g, grid); else launch_major<BNv, ST, false>(ctx, a_mn, b_mn, ta, tb, tc, g, grid); }
+  TALOS_TC_CASE(256, 4, 2) else TALOS_TC_CASE(128, 6, 3) else TALOS_TC_CASE(64, 8, 4) else TALOS_TC_CASE(32, 8, 4)
 #undef TALOS_TC_CASE
   if (splits > 1) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
 }
