@@ -127,21 +127,55 @@ gemm_fp32_kernel(GemmArgs g) {
 
 }  // namespace
 
-// Sums `splits` partial [M,N] slabs in slab order (deterministic) and applies the epilogue.
+// Sums `splits` partial [M,N] slabs (deterministic: fixed assignment, fixed order) and applies the
+// epilogue.  Scalar version for ragged shapes.
 __global__ void talos_splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long M, long long N,
                                            float* C, long long ldc, EpiArgs epi) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= M * N) return;
   long long m = idx / N, n = idx % N;
   float acc = 0.f;
-  for (int s = 0; s < splits; ++s) acc += partial[(long long)s * M * N + idx];
+#pragma unroll 4
+  for (int s = 0; s < splits; ++s) acc += __ldcs(partial + (long long)s * M * N + idx);
   C[m * ldc + n] = talos_epilogue_apply(epi, acc, m, n, C, ldc);
+}
+
+// Vector version: a CTA covers 64 float4 columns x 4 split lanes; lane l sums slabs l, l+4, ... with
+// eight loads in flight, then the four lane sums are added in lane order.
+__global__ void __launch_bounds__(256)
+talos_splitk_reduce_vec_kernel(const float4* __restrict__ partial, int splits, long long MN4, long long N, float* C,
+                               long long ldc, EpiArgs epi) {
+  __shared__ float4 sh[4][64];
+  const int col = threadIdx.x & 63, sl = threadIdx.x >> 6;
+  const long long idx = (long long)blockIdx.x * 64 + col;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (idx < MN4) {
+#pragma unroll 8
+    for (int s = sl; s < splits; s += 4) {
+      const float4 v = __ldcs(partial + (long long)s * MN4 + idx);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+  }
+  sh[sl][col] = acc;
+  __syncthreads();
+  if (sl == 0 && idx < MN4) {
+    float r[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int l = 0; l < 4; ++l) { r[0] += sh[l][col].x; r[1] += sh[l][col].y; r[2] += sh[l][col].z; r[3] += sh[l][col].w; }
+    const long long e = idx * 4, m = e / N, n = e % N;          // N % 4 == 0: the four elements share a row
+#pragma unroll
+    for (int k = 0; k < 4; ++k) C[m * ldc + n + k] = talos_epilogue_apply(epi, r[k], m, n + k, C, ldc);
+  }
 }
 
 void talos_splitk_reduce(talos_ctx* ctx, const float* partial, int splits, int64_t M, int64_t N, float* C,
                          int64_t ldc, const EpiArgs& epi) {
   int64_t total = M * N;
-  talos_splitk_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, ctx->stream>>>(partial, splits, M, N, C, ldc, epi);
+  if ((N & 3) == 0 && (((uintptr_t)partial) & 15) == 0) {
+    talos_splitk_reduce_vec_kernel<<<(unsigned)ceil_div(total / 4, 64), 256, 0, ctx->stream>>>((const float4*)partial, splits, total / 4, N, C, ldc, epi);
+  } else {
+    talos_splitk_reduce_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, ctx->stream>>>(partial, splits, M, N, C, ldc, epi);
+  }
   talos_launched(ctx, "splitk_reduce");
 }
 

@@ -383,8 +383,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // The split is elementwise, so it is oblivious to the swizzle: same offset in, same offset out.
         float4* ahi = (float4*)(sA + stage * A_BYTES); float4* alo = (float4*)(sAlo + stage * A_BYTES);
         float4* bhi = (float4*)(sB + stage * B_BYTES); float4* blo = (float4*)(sBlo + stage * B_BYTES);
-#pragma unroll 4
-        for (int i = ct; i < (A_BYTES + B_BYTES) / 16; i += 128) {
+        constexpr int CONV_ITERS = (A_BYTES + B_BYTES) / 16 / 128;
+#pragma unroll 8
+        for (int ci = 0; ci < CONV_ITERS; ++ci) {
+          const int i = ct + ci * 128;
           float4* hi = i < A_BYTES / 16 ? ahi + i : bhi + (i - A_BYTES / 16);
           float4* lo = i < A_BYTES / 16 ? alo + i : blo + (i - A_BYTES / 16);
           float4 v = *hi, h, l;
@@ -483,7 +485,8 @@ void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, c
 void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
                int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
-  const int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
+  int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
+  if (x3 && bn == 256 && getenv("TALOS_X3_BN128")) bn = 128;
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.m_tiles = (int)ceil_div(M, BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);

@@ -105,23 +105,64 @@ rmsnorm_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x, co
     }
 }
 
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, int nparts, int dim, float* __restrict__ out, int acc) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
+// Sums `nparts` partial rows of length `dim` in part order.  A CTA covers 32 columns x 8 part lanes;
+// lane l sums parts l, l+8, ... then the eight lane sums are added in lane order (deterministic).
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, int nparts, int dim, float* __restrict__ out, int acc) {
+  __shared__ float sh[8][33];
+  const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * dim + c];
-  out[c] = acc ? out[c] + s : s;
+  if (c < dim) {
+#pragma unroll 8
+    for (int p = pl; p < nparts; p += 8) s += partial[(size_t)p * dim + c];
+  }
+  sh[pl][cl] = s;
+  __syncthreads();
+  if (pl == 0 && c < dim) {
+    float t = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) t += sh[l][cl];
+    out[c] = acc ? out[c] + t : t;
+  }
 }
 
-// Column sums of a [rows, n] matrix, stage 1: each CTA sums a contiguous slab of rows.
+// Column sums of a [rows, n] matrix, stage 1, any n: each CTA sums a contiguous slab of rows.
 __global__ void colsum_stage1_kernel(const float* __restrict__ g, long long rows, int n, long long rows_per_cta,
                                      float* __restrict__ partial) {
   long long r0 = (long long)blockIdx.y * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= n) return;
   float s = 0.f;
+#pragma unroll 8
   for (long long r = r0; r < r1; ++r) s += g[r * n + c];
   partial[(size_t)blockIdx.y * n + c] = s;
+}
+
+// Stage 1 for n % 4 == 0 and n <= 1024: 256 threads = (n/4 float4 columns) x (row lanes); every thread
+// streams its rows with eight 128-bit loads in flight; row lanes are combined in lane order.
+__global__ void __launch_bounds__(256)
+colsum_stage1_vec_kernel(const float4* __restrict__ g, long long rows, int n4, long long rows_per_cta,
+                         float* __restrict__ partial) {
+  extern __shared__ float4 shv[];                       // [row_lanes][n4]
+  const int row_lanes = 256 / n4;
+  const int cl = threadIdx.x % n4, rl = threadIdx.x / n4;
+  const long long r0 = (long long)blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (rl < row_lanes) {
+#pragma unroll 8
+    for (long long r = r0 + rl; r < r1; r += row_lanes) {
+      const float4 v = __ldcs(g + r * n4 + cl);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    shv[rl * n4 + cl] = s;
+  }
+  __syncthreads();
+  if (rl == 0) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int l = 0; l < row_lanes; ++l) { const float4 v = shv[l * n4 + cl]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+    ((float4*)partial)[(size_t)blockIdx.x * n4 + cl] = t;
+  }
 }
 
 // ---------------------------------------------------------------- softmax
@@ -244,7 +285,7 @@ TALOS_API talos_status talos_rmsnorm_bwd(talos_ctx* ctx, const float* dy, const 
                                                                         accumulate & 1, partial);
   talos_launched(ctx, "rmsnorm_bwd");
   if (dgamma) {
-    colsum_partials_kernel<<<(unsigned)ceil_div(dim, 128), 128, 0, ctx->stream>>>(partial, grid, (int)dim, dgamma, (accumulate >> 1) & 1);
+    colsum_partials_kernel<<<(unsigned)ceil_div(dim, 32), 256, 0, ctx->stream>>>(partial, grid, (int)dim, dgamma, (accumulate >> 1) & 1);
     talos_launched(ctx, "rmsnorm_dgamma");
   }
   TALOS_ENTRY_END
@@ -255,13 +296,27 @@ TALOS_API talos_status talos_colsum(talos_ctx* ctx, const float* g, float* out, 
   talos_check_ctx(ctx);
   TALOS_REQUIRE(rows >= 0 && n > 0 && n < (1 << 24), TALOS_ERR_SHAPE, "bad colsum shape");
   TALOS_REQUIRE(g && out, TALOS_ERR_ARG, "null pointer");
+  const bool vec = (n % 4 == 0) && n <= 1024 && aligned16(g) && (256 % (n / 4) == 0 || n / 4 <= 256);
+  int64_t slabs;
+  if (vec && 256 / (n / 4) >= 1) {
+    const int n4 = (int)(n / 4);
+    slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 32), 4 * (int64_t)ctx->sm_count));
+    int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
+    float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
+    size_t shmem = sizeof(float4) * (size_t)(256 / n4) * n4;
+    colsum_stage1_vec_kernel<<<(unsigned)slabs, 256, shmem, ctx->stream>>>((const float4*)g, rows, n4, rows_per, partial);
+    talos_launched(ctx, "colsum_stage1");
+    colsum_partials_kernel<<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
+    talos_launched(ctx, "colsum_stage2");
+    return TALOS_OK;
+  }
   int64_t col_blocks = ceil_div(n, 128);
-  int64_t slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 64), (4 * (int64_t)ctx->sm_count) / col_blocks + 1));
+  slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 64), (4 * (int64_t)ctx->sm_count) / col_blocks + 1));
   int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
   float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
   colsum_stage1_kernel<<<dim3((unsigned)col_blocks, (unsigned)slabs), 128, 0, ctx->stream>>>(g, rows, (int)n, rows_per, partial);
   talos_launched(ctx, "colsum_stage1");
-  colsum_partials_kernel<<<(unsigned)col_blocks, 128, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
+  colsum_partials_kernel<<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
   talos_launched(ctx, "colsum_stage2");
   TALOS_ENTRY_END
 }
