@@ -115,6 +115,18 @@ talos_status talos_linear_bwd(talos_ctx* ctx, const float* x, const float* W, co
 /* broadcast_to_batch + Add and its backward column sum (src/autograd.rs:511-547). */
 talos_status talos_bias_add(talos_ctx* ctx, float* y, const float* bias, int64_t rows, int64_t n);
 talos_status talos_colsum(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n, int32_t accumulate);
+/* Same result as talos_colsum for callers that must not allocate (no counterpart in the reference, which
+ * has no device memory to manage).  talos_colsum takes its partial-sum scratch from the context and may
+ * grow it with cudaMalloc, which synchronises the whole device: a trainer thread doing that stalls every
+ * other thread's kernels, and a host that gave all device memory to its own pool has none left to hand out.
+ * This variant keeps the scratch in a fixed 2 MiB array inside the library image (each GPU that loads the
+ * library holds it until the process exits) and never allocates or frees anything.
+ * Limits: n <= 1024 columns; wider input is refused with TALOS_ERR_UNSUPPORTED.
+ * The first call on a device looks up the array's device address; make that call before starting any
+ * stream capture.  All calls share the one array: two calls whose kernels overlap on the GPU (different
+ * streams or contexts) race on it, so keep them on one stream or serialise them.  Nothing in the array has
+ * to be cleared between calls: each call overwrites every element it later reads. */
+talos_status talos_colsum_noalloc(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n, int32_t accumulate);
 
 /* ---- RMSNorm (src/nn.rs:145-304): rms = sqrt(mean(x^2)+eps), y = x/rms*gamma --------------- */
 /* inv_rms [rows] is the only thing saved for backward (x-hat is recomputed). */
