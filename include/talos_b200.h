@@ -68,6 +68,19 @@ int32_t talos_ctx_tensor_cores_active(talos_ctx* ctx);
 /* Number of kernels this library has launched on the ctx since creation. */
 int64_t talos_ctx_launch_count(talos_ctx* ctx);
 
+/* ---- device memory for hosts without a CUDA runtime binding of their own (the storage behind
+ * Tensor.data / Tensor.grad, src/autograd.rs:15-20).  Copies are ordered on the ctx stream; the
+ * *_host copies block until the host buffer may be reused / holds the data. */
+talos_status talos_malloc(talos_ctx* ctx, size_t bytes, void** out);
+talos_status talos_free(talos_ctx* ctx, void* ptr);
+talos_status talos_memset_zero(talos_ctx* ctx, void* ptr, size_t bytes);
+talos_status talos_copy_from_host(talos_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+talos_status talos_copy_to_host(talos_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+talos_status talos_copy_device(talos_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes);
+/* f64 host <-> fp32 device conversion at the Tensor boundary (the crate's Vec<f64>). */
+talos_status talos_upload_f64(talos_ctx* ctx, float* dst_dev, const double* src_host, int64_t n);
+talos_status talos_download_f64(talos_ctx* ctx, double* dst_host, const float* src_dev, int64_t n);
+
 /* ---- GEMM: Tensor::matmul forward and both backward products ------------------------------ */
 /* Optional fused epilogue, applied in this order to acc = op(A).op(B):
  *   v = acc + bias[n];  aux_out[m,n] = v;  v = act(v);  v *= dact(aux_in[m,n]);  C = v + beta*C.

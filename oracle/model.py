@@ -240,6 +240,32 @@ class LuckTransformer:
         h3 = h2 + linear_fwd(f1, *self.ffn_2)
         return linear_fwd(rmsnorm_fwd(h3, self.gf, self.eps)[0], *self.out_proj)
 
+    def forward_backward(self, x, g_out, pos_mode="head_index"):
+        """Forward (:71-90) and the backward the tape would run.  Returns (output, dx, grads) with grads in
+        LuckTransformer::parameters order (:205-215): embed W,b; norm_1; MLA dkv,uk,uv,q,kr,qr,o; norm_2;
+        ffn_1 W,b; ffn_2 W,b; norm_final; out_proj W,b."""
+        B, S, _ = x.shape
+        h = linear_fwd(x, *self.embed)
+        n1, rms1, xh1 = rmsnorm_fwd(h, self.g1, self.eps)
+        att, cache = mla_forward(n1, self.mla, self.cfg, pos_mode, return_cache=True)
+        h2 = h + att
+        n2, rms2, xh2 = rmsnorm_fwd(h2, self.g2, self.eps)
+        z1 = linear_fwd(n2, *self.ffn_1); f1 = act_fwd(z1, "relu")
+        h3 = h2 + linear_fwd(f1, *self.ffn_2)
+        nf, rmsf, xhf = rmsnorm_fwd(h3, self.gf, self.eps)
+        out = linear_fwd(nf, *self.out_proj)
+        d_nf, dWo, dbo = linear_bwd(nf, self.out_proj[0], g_out, True)
+        d_h3, dgf = rmsnorm_bwd(d_nf, self.gf, rmsf, xhf)
+        d_f1, dW2, db2 = linear_bwd(f1, self.ffn_2[0], d_h3, True)
+        d_z1 = act_bwd(d_f1, z1, f1, "relu")
+        d_n2, dW1, db1 = linear_bwd(n2, self.ffn_1[0], d_z1, True)
+        d_h2, dg2 = rmsnorm_bwd(d_n2, self.g2, rms2, xh2); d_h2 = d_h2 + d_h3
+        d_n1, dmla = mla_backward(d_h2, self.mla, self.cfg, cache, pos_mode)
+        d_h, dg1 = rmsnorm_bwd(d_n1, self.g1, rms1, xh1); d_h = d_h + d_h2
+        dx, dWe, dbe = linear_bwd(x, self.embed[0], d_h, True)
+        grads = [dWe, dbe, dg1] + [dmla[k] for k in ("dkv", "uk", "uv", "q", "kr", "qr", "o")] + [dg2, dW1, db1, dW2, db2, dgf, dWo, dbo]
+        return out, dx, grads
+
     def forward_inference_step(self, x, cache, start_pos):
         """forward_inference_step (:152-193): one token through the KV-cached path."""
         lin = linear_forward_inference

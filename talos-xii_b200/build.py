@@ -58,5 +58,23 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def build_host_tests():
+    """Compiles the C++ programs that exercise the host mirror (host/talos.hpp) against the built library."""
+    root = os.path.dirname(HERE)
+    src_dir = os.path.join(root, "tests", "cpp"); out_dir = os.path.join(src_dir, "bin")
+    os.makedirs(out_dir, exist_ok=True)
+    hdr = os.path.join(HERE, "host", "talos.hpp")
+    for name in ("test_reference_kats", "host_driver"):
+        src = os.path.join(src_dir, name + ".cpp"); out = os.path.join(out_dir, name)
+        if os.path.exists(out) and os.path.getmtime(out) > max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(LIB)):
+            continue
+        cmd = ["g++", "-std=c++17", "-O2", "-Wall", "-o", out, src, "-L", HERE, "-ltalos_b200", "-Wl,-rpath," + HERE, "-Wl,-rpath,$ORIGIN/../../../talos-xii_b200"]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("g++ failed for %s:\n%s" % (name, r.stdout))
+    return out_dir
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_host_tests())

@@ -90,6 +90,83 @@ TALOS_API talos_status talos_ctx_reserve_workspace(talos_ctx* ctx, size_t bytes)
 TALOS_API int32_t talos_ctx_tensor_cores_active(talos_ctx* ctx) { return ctx && ctx->tc_state == 1 ? 1 : 0; }
 TALOS_API int64_t talos_ctx_launch_count(talos_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
 
+// ---- device memory for hosts that bind only this ABI ----
+TALOS_API talos_status talos_malloc(talos_ctx* ctx, size_t bytes, void** out) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(out != nullptr, TALOS_ERR_ARG, "null out pointer");
+  *out = nullptr;
+  if (bytes == 0) return TALOS_OK;
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess) { cudaGetLastError(); throw talos_error(TALOS_ERR_ALLOC, "device allocation failed"); }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_free(talos_ctx* ctx, void* ptr) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  if (ptr) { TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream)); TALOS_CHECK_CUDA(cudaFree(ptr)); }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_memset_zero(talos_ctx* ctx, void* ptr, size_t bytes) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  if (bytes) { TALOS_REQUIRE(ptr != nullptr, TALOS_ERR_ARG, "null pointer"); TALOS_CHECK_CUDA(cudaMemsetAsync(ptr, 0, bytes, ctx->stream)); }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_copy_from_host(talos_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  if (bytes) {
+    TALOS_REQUIRE(dst && src, TALOS_ERR_ARG, "null pointer");
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_copy_to_host(talos_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  if (bytes) {
+    TALOS_REQUIRE(dst && src, TALOS_ERR_ARG, "null pointer");
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_copy_device(talos_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  if (bytes) {
+    TALOS_REQUIRE(dst && src, TALOS_ERR_ARG, "null pointer");
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  }
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_upload_f64(talos_ctx* ctx, float* dst, const double* src, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(n >= 0 && ((dst && src) || n == 0), TALOS_ERR_ARG, "null pointer");
+  if (n == 0) return TALOS_OK;
+  std::string buf(sizeof(float) * (size_t)n, '\0');
+  float* f = (float*)&buf[0];
+  for (int64_t i = 0; i < n; ++i) f[i] = (float)src[i];
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(dst, f, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_download_f64(talos_ctx* ctx, double* dst, const float* src, int64_t n) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(n >= 0 && ((dst && src) || n == 0), TALOS_ERR_ARG, "null pointer");
+  if (n == 0) return TALOS_OK;
+  std::string buf(sizeof(float) * (size_t)n, '\0');
+  float* f = (float*)&buf[0];
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(f, src, sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost, ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (int64_t i = 0; i < n; ++i) dst[i] = (double)f[i];
+  TALOS_ENTRY_END
+}
+
 // ---- src/rng.rs:14-117 restated: SplitMix64 seeding, xoshiro256**, 53-bit uniform, Box-Muller z0 ----
 namespace {
 struct Xoshiro {

@@ -1,0 +1,163 @@
+// The reference crate's own unit tests for this path, replayed through the C++ host mirror
+// (talos::Tensor / Module over the C ABI) on the GPU.  Each test names the Rust test it mirrors.
+#include <cmath>
+#include <cstdio>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "../../talos-xii_b200/host/talos.hpp"
+
+using namespace talos;
+static int failures = 0;
+#define EXPECT(cond) do { if (!(cond)) { std::printf("    EXPECT failed: %s (line %d)\n", #cond, __LINE__); ++failures; } } while (0)
+static void run(const char* name, const std::function<void()>& f) {
+  int before = failures;
+  try { f(); } catch (const std::exception& e) { std::printf("    exception: %s\n", e.what()); ++failures; }
+  std::printf("%s %s\n", failures == before ? "[ OK ]" : "[FAIL]", name);
+}
+static bool any_abs_gt(const std::vector<double>& v, double t) { for (double x : v) if (std::fabs(x) > t) return true; return false; }
+
+int main(int argc, char** argv) {
+  if (argc > 1) Runtime::get().mode = std::stoi(argv[1]);
+  std::printf("mode %d\n", Runtime::get().mode);
+
+  run("grad_check::test_autograd_memory_leak_fix", [] {                  // src/grad_check.rs:6-27
+    Tensor a = Tensor::new_({2.0}, {1});
+    Tensor b = a;
+    for (int i = 0; i < 100; ++i) b = b * Tensor::new_({1.1}, {1});
+    EXPECT(b._ctx != nullptr);
+    Tensor c = b.detach(); EXPECT(c._ctx == nullptr);
+    Tensor d = b; d.clear_graph(); EXPECT(d._ctx == nullptr);
+    EXPECT(std::fabs(b.item() - 2.0 * std::pow(1.1, 100)) / b.item() < 1e-4);
+  });
+  run("grad_check::test_grad_check_matmul", [] {                         // src/grad_check.rs:30-63
+    Tensor a = Tensor::new_({2.0, 3.0, 4.0, 5.0}, {2, 2}), x = Tensor::new_({1.0, 2.0}, {2, 1});
+    Tensor y = a.matmul(x); Tensor loss = y.sum(); loss.backward();
+    auto yv = y.to_vec(); EXPECT(yv[0] == 8.0 && yv[1] == 14.0);
+    auto ag = a.grad_vec(), xg = x.grad_vec();
+    EXPECT(std::fabs(xg[0] - 6.0) < 1e-6 && std::fabs(xg[1] - 8.0) < 1e-6);
+    EXPECT(std::fabs(ag[0] - 1.0) < 1e-6 && std::fabs(ag[1] - 2.0) < 1e-6 && std::fabs(ag[2] - 1.0) < 1e-6 && std::fabs(ag[3] - 2.0) < 1e-6);
+  });
+  run("grad_check::test_grad_check_broadcast", [] {                      // src/grad_check.rs:66-90
+    Tensor x = Tensor::new_({1.0, 2.0}, {2}), y = Tensor::new_({10.0}, {1});
+    Tensor z = x + y.broadcast({2}); z.sum().backward();
+    auto zv = z.to_vec(); EXPECT(zv[0] == 11.0 && zv[1] == 12.0);
+    auto xg = x.grad_vec(); EXPECT(std::fabs(xg[0] - 1.0) < 1e-6 && std::fabs(xg[1] - 1.0) < 1e-6);
+    EXPECT(std::fabs(y.grad_vec()[0] - 2.0) < 1e-6);
+  });
+  run("grad_check::test_numerical_gradient_check", [] {                  // src/grad_check.rs:93-114
+    const double xv = 2.0, eps = 1e-6;
+    Tensor x = Tensor::new_({xv}, {1});
+    Tensor y = (x * x) * x.sin(); y.backward();
+    auto f = [](double v) { return v * v * std::sin(v); };
+    EXPECT(std::fabs(x.grad_vec()[0] - (f(xv + eps) - f(xv - eps)) / (2 * eps)) < 1e-4);
+  });
+  run("autograd::test_broadcast_scalar", [] {                            // src/autograd.rs:1869-1875
+    Tensor b = Tensor::new_({5.0}, {1}).broadcast({2, 2});
+    EXPECT((b.shape == std::vector<size_t>{2, 2}));
+    for (double v : b.to_vec()) EXPECT(v == 5.0);
+  });
+  run("autograd: shape errors panic", [] {                               // src/autograd.rs:96-100, :209, :1611
+    bool a = false, b = false, c = false;
+    try { Tensor::new_({1.0, 2.0}, {3}); } catch (const Panic&) { a = true; }
+    try { Tensor::zeros({2, 3}).matmul(Tensor::zeros({4, 2})); } catch (const Panic& e) { b = std::string(e.what()).find("MatMul dimension mismatch") != std::string::npos; }
+    try { Tensor::zeros({2}) + Tensor::zeros({3}); } catch (const Panic& e) { c = std::string(e.what()).find("Add shape mismatch") != std::string::npos; }
+    EXPECT(a && b && c);
+  });
+  run("transformer::test_tensor_reshape", [] {                           // src/transformer.rs:1192-1209: reshape is a copy
+    Tensor t = Tensor::new_({1.0, 2.0, 3.0, 4.0}, {2, 2});
+    Tensor r = t.reshape({4});
+    EXPECT((r.shape == std::vector<size_t>{4}) && r.to_vec()[0] == 1.0);
+    t.set_data({10.0, 2.0, 3.0, 4.0});
+    EXPECT(r.to_vec()[0] == 1.0);
+  });
+  run("transformer::test_tensor_transpose", [] {                         // src/transformer.rs:1212-1225
+    Tensor tt = Tensor::new_({1, 2, 3, 4, 5, 6}, {2, 3}).transpose(0, 1);
+    EXPECT((tt.shape == std::vector<size_t>{3, 2}));
+    EXPECT((tt.to_vec() == std::vector<double>{1, 4, 2, 5, 3, 6}));
+  });
+  run("transformer::test_mla_forward_backward", [] {                     // src/transformer.rs:1228-1266
+    MultiHeadLatentAttention mla(MLAConfig{16, 2, 0, 8, 4, 8, 10}, 42);
+    Tensor input = Tensor::rand({1, 3, 16}, -0.1, 0.1, 123);
+    Tensor out = mla.forward(input);
+    EXPECT((out.shape == std::vector<size_t>{1, 3, 16}));
+    out.mean().backward();
+    double s1 = 0, s2 = 0; for (double g : mla.w_dkv.weight.grad_vec()) s1 += g; for (double g : mla.w_uk.weight.grad_vec()) s2 += g;
+    EXPECT(std::fabs(s1) > 0.0 && std::fabs(s2) > 0.0);
+  });
+  run("transformer::test_rope_backward", [] {                            // src/transformer.rs:1269-1281
+    RoPE rope(4, 10);
+    Tensor x = Tensor::rand({1, 2, 4}, -1.0, 1.0, 123);
+    rope.forward(x, 0).sum().backward();
+    EXPECT(any_abs_gt(x.grad_vec(), 1e-6));
+  });
+  run("transformer::test_rmsnorm_backward", [] {                         // src/transformer.rs:1284-1299
+    RMSNorm norm(4, 1e-5, 123);
+    Tensor x = Tensor::rand({2, 4}, 0.1, 1.0, 123);
+    norm.forward(x).sum().backward();
+    EXPECT(any_abs_gt(x.grad_vec(), 1e-6) && any_abs_gt(norm.weight.grad_vec(), 1e-6));
+  });
+  run("transformer::test_luck_transformer_integration", [] {             // src/transformer.rs:1302-1328
+    LuckTransformer t(8, 8, true, 42);
+    Tensor x = Tensor::rand({1, 5, 8}, -0.1, 0.1, 123);
+    t.forward(x).mean().backward();
+    EXPECT(t.parameters().size() > 10);
+    EXPECT(any_abs_gt(t.embed.weight.grad_vec(), 0.0) && any_abs_gt(t.norm_1.weight.grad_vec(), 0.0));
+  });
+  run("ppo::test_actor_critic_shapes", [] {                              // src/ppo.rs:1074-1093
+    ActorCritic policy(42);
+    Tensor s1 = Tensor::new_(std::vector<double>(8, 0.5), {8});
+    EXPECT(policy.forward_actor(s1).shape == std::vector<size_t>{5} && policy.forward_critic(s1).shape == std::vector<size_t>{1});
+    Tensor s2 = Tensor::new_(std::vector<double>(40, 0.5), {5, 8});
+    EXPECT(policy.forward_actor(s2).shape == std::vector<size_t>{5} && policy.forward_critic(s2).shape == std::vector<size_t>{1});
+    Tensor s3 = Tensor::new_(std::vector<double>(40, 0.5), {1, 5, 8});
+    EXPECT(policy.forward_actor(s3).shape == std::vector<size_t>{5} && policy.forward_critic(s3).shape == std::vector<size_t>{1});
+  });
+  run("ppo: last_token cuts the graph", [] {                             // src/transformer.rs:92-109: only the heads receive gradients
+    ActorCritic policy(7);
+    Tensor s = Tensor::rand({4, 8}, -0.5, 0.5, 3);
+    policy.forward_actor(s).sum().backward();
+    EXPECT(any_abs_gt(policy.actor_head.weight.grad_vec(), 0.0));
+    EXPECT(!any_abs_gt(policy.backbone.embed.weight.grad_vec(), 0.0));
+  });
+  run("sim::ppo_fast_slow_alignment_distribution", [] {                  // src/sim.rs:1181-1216
+    ActorCritic policy(12345);
+    const size_t seq = 6, dim = 8;
+    std::vector<double> flat(seq * dim);
+    for (size_t t = 0; t < seq; ++t) for (size_t i = 0; i < dim; ++i) flat[t * dim + i] = t * 0.01 + i * 0.001;
+    auto softmax = [](const std::vector<double>& l) { double mx = -1e300, s = 0; for (double v : l) mx = std::max(mx, v);
+      std::vector<double> o(l.size()); for (size_t i = 0; i < l.size(); ++i) { o[i] = std::exp(l[i] - mx); s += o[i]; } for (double& v : o) v /= s; return o; };
+    auto slow = softmax(policy.forward_actor(Tensor::new_(flat, {seq, dim})).to_vec());
+    KVCache kv(policy.backbone.mla_layer.config.num_heads); kv.clear();
+    std::vector<double> last;
+    for (size_t t = 0; t < seq; ++t) last = policy.backbone.forward_inference_step(std::vector<double>(flat.begin() + t * dim, flat.begin() + (t + 1) * dim), kv, t);
+    auto fast = softmax(policy.actor_head.forward_inference(last));
+    double diff = 0; for (size_t i = 0; i < 5; ++i) diff += std::fabs(slow[i] - fast[i]);
+    EXPECT(diff < 1e-6);
+    policy.backbone.mla_layer.prune_kv_cache(kv, 4); EXPECT(kv.len == 4);           // sliding window, src/transformer.rs:843-874
+  });
+  run("dqn: dueling network consumer (batch 64) trains", [] {            // src/dqn.rs:68-107, :207-239, :482-584
+    Linear l1(8, 64, true, 1), l2(64, 64, true, 2), val(64, 1, true, 3), adv(64, 5, true, 4);
+    auto fwd = [&](const Tensor& s) {
+      Tensor x = l2.forward(l1.forward(s).relu()).relu();
+      Tensor v = val.forward(x), a = adv.forward(x);
+      Tensor ones15 = Tensor::new_(std::vector<double>(5, 1.0), {1, 5}), fifth = Tensor::new_(std::vector<double>(5, 0.2), {5, 1});
+      return v.matmul(ones15) + a - a.matmul(fifth).matmul(ones15);                  // Q = V + A - mean(A)
+    };
+    std::vector<Tensor> params; for (Linear* l : {&l1, &l2, &val, &adv}) for (auto& p : l->parameters()) params.push_back(p);
+    Adam opt(params, 1e-3); opt.clip_norm = 1.0;
+    Tensor states = Tensor::rand({64, 8}, -1.0, 1.0, 9), target = Tensor::rand({64, 5}, -1.0, 1.0, 10);
+    double first = 0, last = 0;
+    for (int it = 0; it < 30; ++it) {
+      opt.zero_grad();
+      Tensor loss = fwd(states).mse_loss(target);
+      loss.backward(); opt.step();
+      if (it == 0) first = loss.item();
+      last = loss.item();
+    }
+    EXPECT(last < first && std::isfinite(last));
+  });
+  std::printf("%d failure(s)\n", failures);
+  return failures ? 1 : 0;
+}
