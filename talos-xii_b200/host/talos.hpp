@@ -299,6 +299,19 @@ struct RoPE {                                                                   
   }
 };
 
+// Token-position rotation of a [B,S,H,dim] tensor (what the graph-free paths do, src/transformer.rs:583-610),
+// as a tape node; the crate's own autograd path never rotates this way (see RoPE::forward above).
+inline Tensor rope_token(const RoPE& r, const Tensor& x, size_t start_pos) {
+  TALOS_ASSERT(x.shape.size() == 4 && x.shape[3] == r.dim, "rope_token expects [B,S,H,dim]");
+  const size_t B = x.shape[0], S = x.shape[1], H = x.shape[2], dm = r.dim, tl = r.max_len * r.dim / 2;
+  Buf c = r.cos_cache, s = r.sin_cache;
+  Tensor out = Tensor::result(x.shape, {x}, [=](const Tensor& o, const std::vector<Tensor>& p) {
+    check(talos_rope(ctx(), o.g(), p[0].g(), c->dev, s->dev, (int64_t)tl, (int64_t)B, (int64_t)S, (int64_t)H, (int64_t)dm, (int64_t)start_pos, 1, 1));
+  });
+  check(talos_rope(ctx(), x.d(), out.d(), c->dev, s->dev, (int64_t)tl, (int64_t)B, (int64_t)S, (int64_t)H, (int64_t)dm, (int64_t)start_pos, 0, 0));
+  return out;
+}
+
 struct MLAConfig { size_t dim, num_heads, q_lora_rank, kv_lora_rank, qk_rope_dim, v_head_dim, max_seq_len; };   // :9-17
 
 struct KVCache {                                                                    // :400-425, device resident [heads][cap][width]
@@ -309,6 +322,7 @@ struct KVCache {                                                                
 
 struct MultiHeadLatentAttention {                                                   // :375-1184
   MLAConfig config; Linear w_dkv, w_uk, w_uv, w_q, w_kr, w_qr, w_o; RoPE rope;
+  bool token_positions = false;      // false: the crate's autograd-path behaviour (rotation by head index)
   MultiHeadLatentAttention(const MLAConfig& c, uint64_t seed)
       : config(c), w_dkv(c.dim, c.kv_lora_rank, false, seed), w_uk(c.kv_lora_rank, c.num_heads * c.v_head_dim, false, seed + 1),
         w_uv(c.kv_lora_rank, c.num_heads * c.v_head_dim, false, seed + 2), w_q(c.dim, c.num_heads * c.v_head_dim, false, seed + 3),
@@ -319,12 +333,12 @@ struct MultiHeadLatentAttention {                                               
   }
   // Fused node for :508-557: concat(content, rope) -> transpose(1,2) -> Q.K^T -> scale -> softmax -> .V -> transpose back.
   static Tensor attention(const Tensor& qc, const Tensor& qr, const Tensor& kc, const Tensor& kr, const Tensor& v, size_t B, size_t S, size_t H,
-                          size_t dh, size_t dr) {
+                          size_t dh, size_t dr, bool causal = false) {
     const size_t tot = dh + dr, BH = B * H; const float scale = 1.f / std::sqrt((float)tot);
     Buf q = make_buf(BH * S * tot, false), k = make_buf(BH * S * tot, false), vv = make_buf(BH * S * dh, false), probs = make_buf(BH * S * S, false);
     auto pack = [&](const Tensor& a, const Tensor* b, size_t wa, size_t wb, float* dst) {   // [B,S,H,wa](+[B,S,H,wb]) -> [B,H,S,wa+wb]
       Buf cat = make_buf(B * S * H * (wa + wb), false);
-      if (b) check(talos_concat_last(ctx(), a.d(), b->d(), cat->dev, (int64_t)(B * S * H), (int64_t)wa, (int64_t)wb));
+      if (b && wb) check(talos_concat_last(ctx(), a.d(), b->d(), cat->dev, (int64_t)(B * S * H), (int64_t)wa, (int64_t)wb));
       else check(talos_copy_device(ctx(), cat->dev, a.d(), sizeof(float) * a.len()));
       int64_t shp[4] = {(int64_t)B, (int64_t)S, (int64_t)H, (int64_t)(wa + wb)};
       check(talos_transpose(ctx(), cat->dev, dst, shp, 4, 1, 2, 0));
@@ -346,7 +360,7 @@ struct MultiHeadLatentAttention {                                               
       unpack(gq->dev, tot, p[0].g(), p[1].g(), dh, dr); unpack(gk->dev, tot, p[2].g(), p[3].g(), dh, dr); unpack(gv->dev, dh, p[4].g(), nullptr, dh, 0);
     });
     Buf att = make_buf(BH * S * dh, false);
-    check(talos_attention_fwd(ctx(), q->dev, k->dev, vv->dev, att->dev, probs->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale, 0));
+    check(talos_attention_fwd(ctx(), q->dev, k->dev, vv->dev, att->dev, probs->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale, causal ? 1 : 0));
     int64_t bhsd[4] = {(int64_t)B, (int64_t)H, (int64_t)S, (int64_t)dh};
     check(talos_transpose(ctx(), att->dev, out.d(), bhsd, 4, 1, 2, 0));
     Runtime::get().synchronize();
@@ -357,7 +371,8 @@ struct MultiHeadLatentAttention {                                               
     const size_t B = x.shape[0], S = x.shape[1], H = config.num_heads, dh = config.v_head_dim, dr = config.qk_rope_dim;
     Tensor c_kv = w_dkv.forward(x), k_c = w_uk.forward(c_kv), v_c = w_uv.forward(c_kv);
     Tensor k_r = w_kr.forward(x).reshape({B, S, H, dr}), q_c = w_q.forward(x), q_r = w_qr.forward(x).reshape({B, S, H, dr});
-    Tensor k_rot = rope.forward(k_r, 0), q_rot = rope.forward(q_r, 0);              // head-index positions, as the crate does here
+    Tensor k_rot = token_positions ? rope_token(rope, k_r, 0) : rope.forward(k_r, 0);   // head-index positions are what the crate does here
+    Tensor q_rot = token_positions ? rope_token(rope, q_r, 0) : rope.forward(q_r, 0);
     Tensor att = attention(q_c, q_rot, k_c, k_rot, v_c, B, S, H, dh, dr);
     return w_o.forward(att);
   }
@@ -446,6 +461,50 @@ struct LuckTransformer : Module {                                               
     ext(embed.parameters()); ext(norm_1.parameters()); ext(mla_layer.parameters()); ext(norm_2.parameters()); ext(ffn_1.parameters());
     ext(ffn_2.parameters()); ext(norm_final.parameters()); ext(out_proj.parameters()); return p;
   }
+};
+
+// Slices [rows, wa+wb] into ([rows, wa], [rows, wb]) as a tape node (backward = concat of the two gradients).
+inline std::pair<Tensor, Tensor> split_last(const Tensor& x, size_t wa, size_t wb) {
+  TALOS_ASSERT(!x.shape.empty() && x.shape.back() == wa + wb, "split_last width mismatch");
+  const size_t rows = x.len() / (wa + wb);
+  std::vector<size_t> sa = x.shape, sb = x.shape; sa.back() = wa; sb.back() = wb;
+  // one shared node would need two outputs; two nodes, each scattering its own gradient slice, give the same sums
+  Tensor a = Tensor::result(sa, {x}, [rows, wa, wb](const Tensor& o, const std::vector<Tensor>& p) {
+    Buf z = make_buf(rows * wb); Buf cat = make_buf(rows * (wa + wb), false);
+    check(talos_concat_last(ctx(), o.g(), z->dev, cat->dev, (int64_t)rows, (int64_t)wa, (int64_t)wb));
+    check(talos_eltwise_binary(ctx(), TALOS_EW_ADD, p[0].g(), cat->dev, p[0].g(), (int64_t)(rows * (wa + wb))));
+  });
+  Tensor b = Tensor::result(sb, {x}, [rows, wa, wb](const Tensor& o, const std::vector<Tensor>& p) {
+    Buf z = make_buf(rows * wa); Buf cat = make_buf(rows * (wa + wb), false);
+    check(talos_concat_last(ctx(), z->dev, o.g(), cat->dev, (int64_t)rows, (int64_t)wa, (int64_t)wb));
+    check(talos_eltwise_binary(ctx(), TALOS_EW_ADD, p[0].g(), cat->dev, p[0].g(), (int64_t)(rows * (wa + wb))));
+  });
+  check(talos_split_last(ctx(), x.d(), a.d(), b.d(), (int64_t)rows, (int64_t)wa, (int64_t)wb, 0));
+  return {a, b};
+}
+
+// Plain pre-norm multi-head block (not in the crate; the benchmark's config 3) in the crate's residual order
+// (src/transformer.rs:71-90): RMSNorm -> QKV -> RoPE(token) -> causal attention -> W_o -> +res -> RMSNorm -> W_ff1 ->
+// SiLU -> W_ff2 -> +res.  No biases.
+struct TransformerBlock : Module {
+  size_t dim, heads; RMSNorm norm_1, norm_2; Linear w_qkv, w_o, w_ff1, w_ff2; RoPE rope;
+  TransformerBlock(size_t d, size_t h, size_t ff, size_t max_seq, double eps, uint64_t seed)
+      : dim(d), heads(h), norm_1(d, eps, seed), norm_2(d, eps, seed + 1), w_qkv(d, 3 * d, false, seed + 2), w_o(d, d, false, seed + 3),
+        w_ff1(d, ff, false, seed + 4), w_ff2(ff, d, false, seed + 5), rope(d / h, max_seq) {}
+  Tensor forward(const Tensor& x) const override {
+    TALOS_ASSERT(x.shape.size() == 3 && x.shape[2] == dim, "TransformerBlock expects [Batch, Seq, Dim]");
+    const size_t B = x.shape[0], S = x.shape[1], dh = dim / heads;
+    Tensor qkv = w_qkv.forward(norm_1.forward(x));                                  // [B,S,3*dim] laid out [q | k | v]
+    auto [q, kv] = split_last(qkv, dim, 2 * dim);
+    auto [k, v] = split_last(kv, dim, dim);
+    Tensor qr = rope_token(rope, q.reshape({B, S, heads, dh}), 0), kr = rope_token(rope, k.reshape({B, S, heads, dh}), 0);
+    Tensor none = Tensor::zeros({1});
+    Tensor att = MultiHeadLatentAttention::attention(qr, none, kr, none, v, B, S, heads, dh, 0, true);
+    Tensor h2 = x + w_o.forward(att);
+    Tensor f = w_ff1.forward_act(norm_2.forward(h2), TALOS_ACT_SILU);
+    return h2 + w_ff2.forward(f);
+  }
+  std::vector<Tensor> parameters() const override { return {norm_1.weight, w_qkv.weight, w_o.weight, norm_2.weight, w_ff1.weight, w_ff2.weight}; }
 };
 
 struct ActorCritic {                                                                // src/ppo.rs:247-307

@@ -3,6 +3,10 @@
 //   luck  <seed> <B> <S> <in> <hidden> : LuckTransformer forward on LCG input, loss = mean, backward;
 //                                        writes output, x.grad, then every parameter's grad in parameters() order.
 //   mla   <seed> <B> <S>               : MultiHeadLatentAttention (dim16/h2/r8/rope4/dv8) forward/backward, same layout.
+//   block <dumpB> <B>                  : benchmark config 3 (S64 d256 H8 ff1024, N(0,0.02^2) weights seeds 11-14, x seed 10,
+//                                        upstream gradient seed 15); loss = sum(out*G); writes fp32: out, dx (first dumpB
+//                                        samples each), then the six parameter gradients.
+//   mla4  <dumpB> <B> <token>          : benchmark config 4 (S128 d512 r64 H8 dh64 dr32, seeds 20-27) forward; writes fp32 out.
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -13,6 +17,14 @@
 using namespace talos;
 
 static void dump(std::FILE* f, const std::vector<double>& v) { std::fwrite(v.data(), sizeof(double), v.size(), f); }
+static void dump32(std::FILE* f, const std::vector<double>& v, size_t count) {
+  std::vector<float> t(count); for (size_t i = 0; i < count; ++i) t[i] = (float)v[i]; std::fwrite(t.data(), sizeof(float), count, f);
+}
+static Tensor normal(std::vector<size_t> shape, uint64_t seed, float std_dev) {
+  std::vector<float> h(numel(shape)); check(talos_rng_normal_host(seed, 0.f, std_dev, h.data(), (int64_t)h.size()));
+  return Tensor::new_(std::vector<double>(h.begin(), h.end()), std::move(shape));
+}
+static void set_normal(Linear& l, uint64_t seed) { l.weight = normal({l.in_features, l.out_features}, seed, 0.02f); }
 // The crate's LCG fills [-limit, 0) only; w <- 2w + limit spreads the same stream over [-limit, limit) so
 // that the softmax is not saturated and every gradient is well conditioned.
 static void symmetrise(Linear& l) {
@@ -43,6 +55,22 @@ int main(int argc, char** argv) {
       Tensor out = m.forward(x); out.mean().backward();
       dump(f, out.to_vec()); dump(f, x.grad_vec());
       for (auto& p : m.parameters()) dump(f, p.grad_vec());
+    } else if (what == "block") {
+      const size_t dumpB = seed, Bn = B, Sq = 64, D = 256;
+      TransformerBlock blk(D, 8, 1024, Sq, 1e-6, 0);
+      set_normal(blk.w_qkv, 11); set_normal(blk.w_o, 12); set_normal(blk.w_ff1, 13); set_normal(blk.w_ff2, 14);
+      Tensor x = normal({Bn, Sq, D}, 10, 1.f), G = normal({Bn, Sq, D}, 15, 1.f);
+      Tensor out = blk.forward(x); (out * G).sum().backward();
+      dump32(f, out.to_vec(), dumpB * Sq * D); dump32(f, x.grad_vec(), dumpB * Sq * D);
+      for (auto& p : blk.parameters()) dump32(f, p.grad_vec(), p.len());
+    } else if (what == "mla4") {
+      const size_t dumpB = seed, Bn = B, Sq = 128, D = 512;
+      MultiHeadLatentAttention m(MLAConfig{D, 8, 0, 64, 32, 64, 128}, 0);
+      m.token_positions = S != 0;
+      set_normal(m.w_dkv, 21); set_normal(m.w_uk, 22); set_normal(m.w_uv, 23); set_normal(m.w_q, 24); set_normal(m.w_kr, 25); set_normal(m.w_qr, 26); set_normal(m.w_o, 27);
+      Tensor x = normal({Bn, Sq, D}, 20, 1.f);
+      Tensor out = m.forward(x);
+      dump32(f, out.to_vec(), dumpB * Sq * D);
     } else { return 4; }
     std::fclose(f);
   } catch (const std::exception& e) { std::fprintf(stderr, "host_driver: %s\n", e.what()); return 1; }

@@ -21,6 +21,14 @@ def test_reference_unit_tests_through_host_mirror(mode):
     assert r.returncode == 0 and "0 failure(s)" in r.stdout, r.stdout
 
 
+def run_driver32(args):
+    with tempfile.NamedTemporaryFile(suffix=".bin") as f:
+        r = subprocess.run([os.path.join(BIN, "host_driver")] + [str(a) for a in args[:2]] + [f.name] + [str(a) for a in args[2:]],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=1200)
+        assert r.returncode == 0, r.stdout
+        return np.fromfile(f.name, dtype=np.float32).astype(np.float64)
+
+
 def run_driver(args, symmetric=True):
     env = dict(os.environ)
     if symmetric: env["TALOS_SYMMETRIC_WEIGHTS"] = "1"
@@ -78,3 +86,55 @@ def test_mla_gradients_match_oracle():
     got = split(flat, [t.shape for t in ref])
     for a, b in zip(got, ref):
         assert np.linalg.norm(a - b) <= 2e-5 * np.linalg.norm(b)
+
+
+def nrm(seed, shape, std=1.0):
+    return orc.f32r(orc.rng_normal(seed, shape, 0.0, 1.0) * np.float64(np.float32(std))) if False else orc.rng_normal(seed, shape, 0.0, std).astype(np.float32).astype(np.float64)
+
+
+@pytest.mark.parametrize("mode,tol", [(1, 1e-5), (2, 2e-3)])
+def test_config3_transformer_block_forward_backward(mode, tol):
+    # BASELINE config 3 shapes (S64 d256 H8 dh32 ff1024, eps 1e-6, RoPE base 10000 token positions, causal, SiLU);
+    # the oracle runs a 32-sample batch, the GPU also the full 1024-sample batch.
+    Bs, S, D, H = 32, 64, 256, 8
+    P = dict(g1=np.ones(D), g2=np.ones(D), w_qkv=nrm(11, (D, 3 * D), 0.02), w_o=nrm(12, (D, D), 0.02), w_ff1=nrm(13, (D, 1024), 0.02),
+             w_ff2=nrm(14, (1024, D), 0.02))
+    x = nrm(10, (Bs, S, D)); G = nrm(15, (Bs, S, D))
+    # the block lays QKV out as [q | k | v] per token; the oracle block as [3, H, dh] per token: same thing
+    y, cache = om.block_fwd(x, P, H, eps=1e-6)
+    dx, dP = om.block_bwd(G, P, cache)
+    flat = run_driver32(["block", mode, Bs, Bs, 0])
+    ref = [y, dx, dP["g1"], dP["w_qkv"], dP["w_o"], dP["g2"], dP["w_ff1"], dP["w_ff2"]]
+    got = split(flat, [t.shape for t in ref])
+    for n, a, b in zip(["out", "dx", "dg1", "dWqkv", "dWo", "dg2", "dWff1", "dWff2"], got, ref):
+        err = np.linalg.norm(a - b) / np.linalg.norm(b)
+        assert err <= 2 * tol, (n, err)          # fp32 dump of the result adds up to 6e-8; gradients chain ~10 GEMMs
+    if mode == 1:
+        # full configuration (batch 1024): samples are independent, so its first 32 samples must reproduce the small run
+        full = run_driver32(["block", mode, Bs, 1024, 0])
+        gf = split(full, [t.shape for t in ref])
+        assert np.linalg.norm(gf[0] - got[0]) <= tol * np.linalg.norm(got[0])
+        assert np.linalg.norm(gf[1] - got[1]) <= tol * np.linalg.norm(got[1])
+        assert np.all(np.isfinite(full))
+
+
+@pytest.mark.parametrize("mode,tol", [(1, 1e-5), (2, 2e-3)])
+def test_config4_mla_forward_both_position_modes(mode, tol):
+    # BASELINE config 4 shapes: S128 d512 latent 64, 8 heads of 64 + rope 32, N(0,0.02^2) weights, non-causal
+    Bs, S, D = 16, 128, 512
+    cfg = om.MLAConfig(D, 8, 64, 32, 64, 128)
+    shapes = dict(dkv=(D, 64), uk=(64, 512), uv=(64, 512), q=(D, 512), kr=(D, 256), qr=(D, 256), o=(512, D))
+    W = {k: nrm(21 + i, shapes[k], 0.02) for i, k in enumerate(["dkv", "uk", "uv", "q", "kr", "qr", "o"])}
+    x = nrm(20, (Bs, S, D))
+    outs = {}
+    for token in (1, 0):
+        ref = om.mla_forward(x, W, cfg, "token" if token else "head_index")
+        got = run_driver32(["mla4", mode, Bs, Bs, token]).reshape(ref.shape)
+        err = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+        assert err <= tol, (token, err)
+        outs[token] = got
+    assert np.linalg.norm(outs[0] - outs[1]) > 1e-3 * np.linalg.norm(outs[1])    # the two conventions really differ here
+    if mode == 1:
+        full = run_driver32(["mla4", mode, Bs, 512, 1]).reshape(outs[1].shape)    # full batch 512: first samples unchanged
+        # (tile shapes and split-K differ with the batch size, so agreement is to the mode's tolerance, not bit-exact)
+        assert np.linalg.norm(full - outs[1]) <= tol * np.linalg.norm(outs[1])
