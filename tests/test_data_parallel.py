@@ -1,0 +1,71 @@
+"""Data-parallel PPO update: G ranks x n samples must equal one rank x G*n samples.
+
+CPU part (gloo, world_size 2): the exchange protocol itself -- local gradient SUMS plus a {loss, kl, count} tail,
+one all-reduce per optimizer step, division by the global count, identical Adam on every rank -- driven with the
+oracle's gradients.  GPU part (needs >= 2 devices): the library's trainer with its NCCL exchange."""
+import os
+import socket
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return str(p)
+
+
+def launch(kind, world, env=None):
+    port = free_port(); outs = []; procs = []
+    d = tempfile.mkdtemp()
+    for r in range(world):
+        out = os.path.join(d, "r%d.npz" % r); outs.append(out)
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), kind, str(r), str(world), port, out],
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=dict(os.environ, **(env or {}))))
+    logs = [p.communicate(timeout=900)[0] for p in procs]
+    for p, log in zip(procs, logs):
+        assert p.returncode == 0, log
+    return [dict(np.load(o)) for o in outs]
+
+
+def single_rank_reference():
+    sys.path.insert(0, HERE)
+    import dp_worker as w
+    import oracle as orc
+    from oracle import model as om
+    obs, act, adv, ret, params = w.problem()
+    model = om.MlpActorCritic(params)
+    old = orc.f32r(model.log_prob(obs, act))
+    kls, _ = om.ppo_update(model, obs, act, old, adv, ret, w.EPOCHS, w.MB, lr=np.float64(np.float32(3e-4)))
+    return model.p, kls
+
+
+def test_two_gloo_ranks_equal_one_rank_on_the_global_batch():
+    ref, ref_kls = single_rank_reference()
+    res = launch("cpu", 2)
+    for k in ref:
+        assert np.array_equal(res[0][k], res[1][k]), "ranks diverged: " + k        # identical Adam on identical reduced gradients
+        assert np.allclose(res[0][k], ref[k], rtol=1e-9, atol=1e-12), k
+    assert np.allclose(res[0]["kls"], ref_kls, rtol=1e-9)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1])
+def test_two_gpu_ranks_equal_one_gpu_rank_and_the_oracle(mode):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ref, ref_kls = single_rank_reference()
+    env = {"TALOS_TEST_MODE": str(mode), "NCCL_NVLS_ENABLE": "0"}
+    two = launch("gpu", 2, env); one = launch("gpu", 1, env)
+    for k in ref:
+        assert np.array_equal(two[0][k], two[1][k]), "ranks diverged: " + k
+        d = np.linalg.norm(ref[k]); d = d if d > 0 else 1.0
+        assert np.linalg.norm(two[0][k] - one[0][k].reshape(two[0][k].shape)) <= 1e-5 * max(np.linalg.norm(one[0][k]), 1e-3), k
+        if k.startswith("w"):
+            assert np.linalg.norm(two[0][k] - ref[k].reshape(two[0][k].shape)) <= 1e-5 * d, k
+    assert np.allclose(two[0]["kls"], ref_kls, rtol=1e-3, atol=1e-8)
