@@ -19,6 +19,8 @@ struct talos_ppo {
   float* step_stats;                   // [max_steps][4] copy of the tail after each step's exchange
   int64_t t = 0; int64_t steps_in_epoch = 0; int64_t last_launches = 0;
   std::vector<float> host_tmp;
+  cudaStream_t copy_stream = nullptr;  // host->device staging of talos_ppo_update_host, overlapped with the steps
+  std::vector<cudaEvent_t> chunk_ready; cudaEvent_t staging_free = nullptr;
 };
 
 namespace {
@@ -125,8 +127,11 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   p->last_launches = ctx->launches.load() - l0;
 }
 
+// `ready` (optional): one event per minibatch that the first epoch's step must wait for (its transitions are
+// still being copied in on another stream).
 void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions, const float* old_logp, const float* adv,
-            const float* ret, int64_t N, int32_t epochs, float kl_stop, float* epoch_kl, int32_t* epochs_run) {
+            const float* ret, int64_t N, int32_t epochs, float kl_stop, float* epoch_kl, int32_t* epochs_run,
+            const std::vector<cudaEvent_t>* ready = nullptr) {
   const int64_t mb = p->cfg.minibatch;
   int32_t done = 0;
   std::vector<float> stats;
@@ -134,6 +139,7 @@ void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* act
     p->steps_in_epoch = 0;
     for (int64_t s = 0; s < N; s += mb) {
       int64_t n = std::min(mb, N - s);
+      if (ready && e == 0) TALOS_CHECK_CUDA(cudaStreamWaitEvent(p->ctx->stream, (*ready)[(size_t)(s / mb)], 0));
       step(p, comm, obs + s * p->cfg.obs_dim, actions + s, old_logp + s, adv + s, ret + s, n);
       TALOS_REQUIRE(p->steps_in_epoch <= MAX_STEPS_PER_EPOCH, TALOS_ERR_UNSUPPORTED, "too many minibatches per epoch");
     }
@@ -187,6 +193,9 @@ TALOS_API talos_status talos_ppo_destroy(talos_ppo* p) {
   if (!p) return TALOS_OK;
   cudaSetDevice(p->ctx->device); cudaStreamSynchronize(p->ctx->stream);
   for (float* q : {p->params, p->grads, p->m, p->v, p->h1, p->h2, p->dh1, p->dh2, p->z, p->dz, p->step_stats}) cudaFree(q);
+  for (cudaEvent_t ev : p->chunk_ready) cudaEventDestroy(ev);
+  if (p->staging_free) cudaEventDestroy(p->staging_free);
+  if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
   delete p;
   TALOS_ENTRY_END
 }
@@ -294,13 +303,29 @@ TALOS_API talos_status talos_ppo_update_host(talos_ppo* p, talos_comm* comm, con
   char* base = (char*)talos_workspace2(p->ctx, bytes);
   float* obs = (float*)base; int32_t* actions = (int32_t*)(obs + N * O);
   float* old_logp = (float*)(actions + N); float* adv = old_logp + N; float* ret = adv + N;
-  cudaStream_t s = p->ctx->stream;
-  TALOS_CHECK_CUDA(cudaMemcpyAsync(obs, obs_h, sizeof(float) * (size_t)(N * O), cudaMemcpyHostToDevice, s));
-  TALOS_CHECK_CUDA(cudaMemcpyAsync(actions, actions_h, sizeof(int32_t) * (size_t)N, cudaMemcpyHostToDevice, s));
-  TALOS_CHECK_CUDA(cudaMemcpyAsync(old_logp, old_logp_h, sizeof(float) * (size_t)N, cudaMemcpyHostToDevice, s));
-  TALOS_CHECK_CUDA(cudaMemcpyAsync(adv, adv_h, sizeof(float) * (size_t)N, cudaMemcpyHostToDevice, s));
-  TALOS_CHECK_CUDA(cudaMemcpyAsync(ret, ret_h, sizeof(float) * (size_t)N, cudaMemcpyHostToDevice, s));
-  update(p, comm, obs, actions, old_logp, adv, ret, N, epochs, kl_stop, epoch_kl_host, epochs_run_out);
+  // Copies run minibatch by minibatch on their own stream; the step on minibatch i waits only for chunk i, so
+  // the transfer of chunk i+1 overlaps the compute of chunk i (pinned host memory makes the copies asynchronous).
+  if (!p->copy_stream) {
+    TALOS_CHECK_CUDA(cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
+    TALOS_CHECK_CUDA(cudaEventCreateWithFlags(&p->staging_free, cudaEventDisableTiming));
+  }
+  const int64_t mb = p->cfg.minibatch, chunks = (N + mb - 1) / mb;
+  while ((int64_t)p->chunk_ready.size() < chunks) {
+    cudaEvent_t ev; TALOS_CHECK_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)); p->chunk_ready.push_back(ev);
+  }
+  cudaStream_t cs = p->copy_stream;
+  TALOS_CHECK_CUDA(cudaEventRecord(p->staging_free, p->ctx->stream));        // earlier work may still read the staging buffer
+  TALOS_CHECK_CUDA(cudaStreamWaitEvent(cs, p->staging_free, 0));
+  for (int64_t c = 0; c < chunks; ++c) {
+    const int64_t s0 = c * mb, n = std::min(mb, N - s0);
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(obs + s0 * O, obs_h + s0 * O, sizeof(float) * (size_t)(n * O), cudaMemcpyHostToDevice, cs));
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(actions + s0, actions_h + s0, sizeof(int32_t) * (size_t)n, cudaMemcpyHostToDevice, cs));
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(old_logp + s0, old_logp_h + s0, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, cs));
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(adv + s0, adv_h + s0, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, cs));
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(ret + s0, ret_h + s0, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, cs));
+    TALOS_CHECK_CUDA(cudaEventRecord(p->chunk_ready[(size_t)c], cs));
+  }
+  update(p, comm, obs, actions, old_logp, adv, ret, N, epochs, kl_stop, epoch_kl_host, epochs_run_out, &p->chunk_ready);
   TALOS_ENTRY_END
 }
 
