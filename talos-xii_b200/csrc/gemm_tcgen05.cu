@@ -417,6 +417,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
+// Dense copy of a [rows][cols] matrix (pitch ld) rounded to TF32 with round-to-nearest.  In the fast TF32
+// mode the tensor core TRUNCATES its fp32 inputs, a bias of ~3.5e-4 per operand; pre-rounding the small operand
+// (the weights) removes its half of that bias for a few microseconds of extra work.
+__global__ void round_tf32_kernel(const float* __restrict__ in, long long ld, int rows, int cols, int out_ld, float* __restrict__ out) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)rows * out_ld) return;
+  int r = (int)(idx / out_ld), c = (int)(idx % out_ld);
+  out[idx] = c < cols ? __uint_as_float(cvt_tf32(in[(long long)r * ld + c])) : 0.f;
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -503,7 +513,21 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   if (x3 && g.kb_per_split > 512 / BK) g.kb_per_split = 512 / BK;
   splits = (int)ceil_div(g.kb_total, g.kb_per_split);
   g.splits = splits;
-  if (splits > 1) g.partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)splits * M * N);
+  // kernel-level scratch: [split-K partials][TF32-rounded copy of the small operand]
+  const int64_t a_rows = a_mn ? K : M, a_cols = a_mn ? M : K, b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
+  const int64_t a_elems = a_rows * a_cols, b_elems = b_rows * b_cols;
+  const bool round_a = !x3 && a_elems <= b_elems && a_elems <= (1 << 20), round_b = !x3 && !round_a && b_elems <= (1 << 20);
+  const int64_t r_rows = round_a ? a_rows : b_rows, r_cols = round_a ? a_cols : b_cols, r_ld = (r_cols + 3) & ~int64_t(3);
+  const size_t partial_bytes = splits > 1 ? ((sizeof(float) * (size_t)splits * M * N + 255) & ~size_t(255)) : 0;
+  const size_t round_bytes = (round_a || round_b) ? sizeof(float) * (size_t)(r_rows * r_ld) : 0;
+  char* scratch = (partial_bytes + round_bytes) ? (char*)talos_workspace(ctx, partial_bytes + round_bytes) : nullptr;
+  if (splits > 1) g.partial = (float*)scratch;
+  if (round_a || round_b) {
+    float* dst = (float*)(scratch + partial_bytes);
+    round_tf32_kernel<<<(unsigned)ceil_div(r_rows * r_ld, 256), 256, 0, ctx->stream>>>(round_a ? A : B, round_a ? lda : ldb, (int)r_rows, (int)r_cols, (int)r_ld, dst);
+    talos_launched(ctx, "round_tf32");
+    if (round_a) { A = dst; lda = r_ld; } else { B = dst; ldb = r_ld; }
+  }
 
   CUtensorMap ta, tb;
   bool ok = a_mn ? make_tmap(&ta, A, K, M, lda, BK, true) : make_tmap(&ta, A, M, K, lda, BM, false);

@@ -105,6 +105,59 @@ rmsnorm_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x, co
     }
 }
 
+// Vector variant (dim % 4 == 0, dim <= 1024, 16-byte aligned): the dy and x rows stay in registers between the
+// reduction and the update, and each lane keeps its dgamma partials in registers across all the rows of its warp.
+template <int NVEC>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+rmsnorm_bwd_vec_kernel(const float4* __restrict__ dy, const float4* __restrict__ x, const float4* __restrict__ gamma,
+                       const float* __restrict__ inv_rms, long long rows, int dim4, float4* __restrict__ dx, int acc_dx,
+                       float* __restrict__ partial) {
+  extern __shared__ float sh[];            // [WARPS_PER_CTA][dim]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + w;
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  float4 gam[NVEC], dg[NVEC];
+#pragma unroll
+  for (int v = 0; v < NVEC; ++v) { int c = lane + v * 32; gam[v] = c < dim4 ? __ldg(gamma + c) : make_float4(0, 0, 0, 0); dg[v] = make_float4(0, 0, 0, 0); }
+  const float inv_dim = 1.f / (float)(dim4 * 4);
+  for (long long r = warp; r < rows; r += nwarps) {
+    const float inv = inv_rms[r];
+    float4 g4[NVEC], x4[NVEC]; float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < NVEC; ++v) {
+      int c = lane + v * 32;
+      g4[v] = c < dim4 ? __ldcs(dy + r * dim4 + c) : make_float4(0, 0, 0, 0);
+      x4[v] = c < dim4 ? __ldcs(x + r * dim4 + c) : make_float4(0, 0, 0, 0);
+      x4[v].x *= inv; x4[v].y *= inv; x4[v].z *= inv; x4[v].w *= inv;               // x-hat
+      dot += g4[v].x * gam[v].x * x4[v].x + g4[v].y * gam[v].y * x4[v].y + g4[v].z * gam[v].z * x4[v].z + g4[v].w * gam[v].w * x4[v].w;
+    }
+    dot = warp_sum(dot) * inv_dim;
+#pragma unroll
+    for (int v = 0; v < NVEC; ++v) {
+      int c = lane + v * 32;
+      if (c < dim4) {
+        if (dx) {
+          float4 o;
+          o.x = inv * (g4[v].x * gam[v].x - x4[v].x * dot); o.y = inv * (g4[v].y * gam[v].y - x4[v].y * dot);
+          o.z = inv * (g4[v].z * gam[v].z - x4[v].z * dot); o.w = inv * (g4[v].w * gam[v].w - x4[v].w * dot);
+          if (acc_dx) { const float4 old = dx[r * dim4 + c]; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+          __stcs(dx + r * dim4 + c, o);
+        }
+        dg[v].x += g4[v].x * x4[v].x; dg[v].y += g4[v].y * x4[v].y; dg[v].z += g4[v].z * x4[v].z; dg[v].w += g4[v].w * x4[v].w;
+      }
+    }
+  }
+  if (!partial) return;
+#pragma unroll
+  for (int v = 0; v < NVEC; ++v) { int c = lane + v * 32; if (c < dim4) ((float4*)(sh + (size_t)w * dim4 * 4))[c] = dg[v]; }
+  __syncthreads();
+  for (int c = threadIdx.x; c < dim4 * 4; c += blockDim.x) {
+    float t = 0.f;
+    for (int i = 0; i < WARPS_PER_CTA; ++i) t += sh[(size_t)i * dim4 * 4 + c];
+    partial[(size_t)blockIdx.x * dim4 * 4 + c] = t;
+  }
+}
+
 // Sums `nparts` partial rows of length `dim` in part order.  A CTA covers 32 columns x 8 part lanes;
 // lane l sums parts l, l+8, ... then the eight lane sums are added in lane order (deterministic).
 __global__ void __launch_bounds__(256)
@@ -193,6 +246,64 @@ softmax_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, long long
   }
 }
 
+// Vector variant for row lengths 32*VEC*NV with 8*VEC-byte aligned rows: each lane owns NV chunks of VEC
+// consecutive columns, so a warp moves 128*VEC bytes per load instruction.
+template <int VEC> struct VecT;
+template <> struct VecT<2> { using T = float2; };
+template <> struct VecT<4> { using T = float4; };
+template <int VEC> __device__ __forceinline__ void vec_to_arr(const typename VecT<VEC>::T& v, float* a);
+template <> __device__ __forceinline__ void vec_to_arr<2>(const float2& v, float* a) { a[0] = v.x; a[1] = v.y; }
+template <> __device__ __forceinline__ void vec_to_arr<4>(const float4& v, float* a) { a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
+template <int VEC> __device__ __forceinline__ typename VecT<VEC>::T arr_to_vec(const float* a);
+template <> __device__ __forceinline__ float2 arr_to_vec<2>(const float* a) { return make_float2(a[0], a[1]); }
+template <> __device__ __forceinline__ float4 arr_to_vec<4>(const float* a) { return make_float4(a[0], a[1], a[2], a[3]); }
+
+// Short rows: LPR lanes per row (a warp handles 32/LPR rows at once), NV float4 per lane, so the two
+// reductions cost log2(LPR) shuffles for 32/LPR rows instead of 5 per row -- shuffle issue, not HBM, is what
+// limits a one-row-per-warp softmax on 64-wide rows.
+template <int LPR, int NV>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+softmax_fwd_vec_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, float scale, int causal_period) {
+  constexpr int LEN = LPR * 4 * NV, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
+  const long long warp = (long long)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * WARPS_PER_CTA;
+  for (long long r0 = warp * RPW; r0 < rows; r0 += nwarps * RPW) {
+    const long long r = r0 + sub;
+    const bool ok = r < rows;
+    const int lim = causal_period > 0 ? (int)(r % causal_period) + 1 : LEN;
+    float4 v[NV]; float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      v[i] = ok ? __ldcs((const float4*)(x + r * LEN) + i * LPR + l) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int c = (i * LPR + l) * 4;
+      v[i].x = c + 0 < lim ? v[i].x * scale : -INFINITY; v[i].y = c + 1 < lim ? v[i].y * scale : -INFINITY;
+      v[i].z = c + 2 < lim ? v[i].z * scale : -INFINITY; v[i].w = c + 3 < lim ? v[i].w * scale : -INFINITY;
+      mx = fmaxf(fmaxf(mx, fmaxf(v[i].x, v[i].y)), fmaxf(v[i].z, v[i].w));
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * LPR + l) * 4;
+      v[i].x = c + 0 < lim ? expf(v[i].x - mx) : 0.f; v[i].y = c + 1 < lim ? expf(v[i].y - mx) : 0.f;
+      v[i].z = c + 2 < lim ? expf(v[i].z - mx) : 0.f; v[i].w = c + 3 < lim ? expf(v[i].w - mx) : 0.f;
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        v[i].x *= inv; v[i].y *= inv; v[i].z *= inv; v[i].w *= inv;
+        __stcs((float4*)(y + r * LEN) + i * LPR + l, v[i]);
+      }
+    }
+  }
+}
+
 template <int NPL>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 softmax_bwd_kernel(const float* __restrict__ y, const float* dy, float* dx, long long rows,
@@ -218,7 +329,7 @@ softmax_bwd_kernel(const float* __restrict__ y, const float* dy, float* dx, long
 }
 
 // ---------------------------------------------------------------- RoPE
-// One thread per interleaved pair (2i, 2i+1) of a [outer, npos, inner, dim] tensor.
+// One thread per interleaved pair (2i, 2i+1) of a [outer, npos, inner, dim] tensor (any even dim).
 __global__ void rope_kernel(const float2* __restrict__ x, float2* __restrict__ y, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, long long table_len, long long total_pairs, int npos,
                             int inner, int half, long long start_pos, int inverse, int acc) {
@@ -237,6 +348,28 @@ __global__ void rope_kernel(const float2* __restrict__ x, float2* __restrict__ y
   }
   if (acc) { float2 old = y[idx]; o.x += old.x; o.y += old.y; }
   y[idx] = o;
+}
+// dim % 4 == 0, fewer than 2^31 pairs, 16-byte aligned buffers: one thread per TWO pairs (a 128-bit access),
+// 32-bit index arithmetic, grid-stride loop.
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(const float4* __restrict__ x, float4* __restrict__ y, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                unsigned table_len, unsigned total_quads, unsigned npos, unsigned inner, unsigned quads_per_row, unsigned start_pos,
+                int inverse, int acc) {
+  for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_quads; idx += gridDim.x * blockDim.x) {
+    const unsigned qi = idx % quads_per_row, rest = idx / quads_per_row;
+    const unsigned p = (rest / inner) % npos;
+    const unsigned toff = (start_pos + p) * (quads_per_row * 2);
+    const float4 v = __ldcs(x + idx); float4 o;
+    if (toff >= table_len) { o = v; }
+    else {
+      const float2 c = __ldg((const float2*)(cos_t + toff) + qi); float2 s = __ldg((const float2*)(sin_t + toff) + qi);
+      if (inverse) { s.x = -s.x; s.y = -s.y; }
+      o.x = v.x * c.x - v.y * s.x; o.y = v.x * s.x + v.y * c.x;
+      o.z = v.z * c.y - v.w * s.y; o.w = v.z * s.y + v.w * c.y;
+    }
+    if (acc) { const float4 old = y[idx]; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+    __stcs(y + idx, o);
+  }
 }
 
 int row_grid(talos_ctx* ctx, int64_t rows) {
@@ -281,6 +414,13 @@ TALOS_API talos_status talos_rmsnorm_bwd(talos_ctx* ctx, const float* dy, const 
   int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, WARPS_PER_CTA), (int64_t)ctx->sm_count * 4));
   float* partial = dgamma ? (float*)talos_workspace(ctx, sizeof(float) * (size_t)grid * dim) : nullptr;
   size_t shmem = sizeof(float) * WARPS_PER_CTA * (size_t)dim;
+  if (dim % 4 == 0 && dim <= 32 * 4 * MAX_VEC && aligned16(dy) && aligned16(x) && aligned16(gamma) && (!dx || aligned16(dx))) {
+    const int dim4 = (int)(dim / 4), nvec = (int)ceil_div(dim4, 32);
+    auto DY = (const float4*)dy; auto X = (const float4*)x; auto G = (const float4*)gamma; auto DX = (float4*)dx;
+#define TALOS_RB_CASE(NV) case NV: rmsnorm_bwd_vec_kernel<NV><<<grid, WARPS_PER_CTA * 32, shmem, ctx->stream>>>(DY, X, G, inv_rms, rows, dim4, DX, accumulate & 1, partial); break;
+    switch (nvec) { TALOS_RB_CASE(1) TALOS_RB_CASE(2) TALOS_RB_CASE(3) TALOS_RB_CASE(4) TALOS_RB_CASE(5) TALOS_RB_CASE(6) TALOS_RB_CASE(7) TALOS_RB_CASE(8) }
+#undef TALOS_RB_CASE
+  } else
   rmsnorm_bwd_kernel<<<grid, WARPS_PER_CTA * 32, shmem, ctx->stream>>>(dy, x, gamma, inv_rms, rows, (int)dim, dx,
                                                                         accumulate & 1, partial);
   talos_launched(ctx, "rmsnorm_bwd");
@@ -328,7 +468,16 @@ TALOS_API talos_status talos_softmax_fwd(talos_ctx* ctx, const float* x, float* 
   TALOS_REQUIRE(rows >= 0 && len >= 0 && len <= 1024, TALOS_ERR_SHAPE, "softmax row length must be <= 1024");
   if (rows == 0 || len == 0) return TALOS_OK;       // an empty row sums to 0 (src/simd.rs:335-337)
   TALOS_REQUIRE(x && y, TALOS_ERR_ARG, "null pointer");
-  int grid = row_grid(ctx, rows); int npl = (int)ceil_div(len, 32);
+  int grid = row_grid(ctx, len <= 128 ? ceil_div(rows, 4) : rows); int npl = (int)ceil_div(len, 32);
+  if (aligned16(x) && aligned16(y) && (len == 64 || len == 128 || len == 256 || len == 512)) {
+    const int cp = (int)causal_period;
+    if (len == 64) softmax_fwd_vec_kernel<8, 2><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, scale, cp);
+    else if (len == 128) softmax_fwd_vec_kernel<8, 4><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, scale, cp);
+    else if (len == 256) softmax_fwd_vec_kernel<16, 4><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, scale, cp);
+    else softmax_fwd_vec_kernel<32, 4><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, scale, cp);
+    talos_launched(ctx, "softmax_fwd");
+    return TALOS_OK;
+  }
 #define TALOS_SM_CASE(NP) if (npl <= NP) softmax_fwd_kernel<NP><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, (int)len, scale, (int)causal_period); else
   TALOS_SM_CASE(1) TALOS_SM_CASE(2) TALOS_SM_CASE(4) TALOS_SM_CASE(8) TALOS_SM_CASE(16)
   softmax_fwd_kernel<32><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>(x, y, rows, (int)len, scale, (int)causal_period);
@@ -383,6 +532,15 @@ TALOS_API talos_status talos_rope(talos_ctx* ctx, const float* x, float* y, cons
   if (pairs == 0) return TALOS_OK;
   TALOS_REQUIRE(x && y && cos_t && sin_t, TALOS_ERR_ARG, "null pointer");
   TALOS_REQUIRE(((uintptr_t)x & 7) == 0 && ((uintptr_t)y & 7) == 0, TALOS_ERR_ARG, "RoPE buffers must be 8-byte aligned");
+  if (dim % 4 == 0 && pairs < (1LL << 31) && aligned16(x) && aligned16(y) && ((uintptr_t)cos_t % 8 == 0) && ((uintptr_t)sin_t % 8 == 0) &&
+      table_len < (1LL << 31) && start_pos + npos < (1LL << 20)) {
+    const unsigned quads = (unsigned)(pairs / 2);
+    const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(quads, 256), (int64_t)ctx->sm_count * 16);
+    rope_vec_kernel<<<grid, 256, 0, ctx->stream>>>((const float4*)x, (float4*)y, cos_t, sin_t, (unsigned)table_len, quads, (unsigned)npos,
+                                                   (unsigned)inner, (unsigned)(dim / 4), (unsigned)start_pos, inverse ? 1 : 0, accumulate ? 1 : 0);
+    talos_launched(ctx, "rope");
+    return TALOS_OK;
+  }
   rope_kernel<<<(unsigned)ceil_div(pairs, 256), 256, 0, ctx->stream>>>((const float2*)x, (float2*)y, cos_t, sin_t, table_len,
                                                                         pairs, (int)npos, (int)inner, (int)(dim / 2), start_pos,
                                                                         inverse ? 1 : 0, accumulate ? 1 : 0);

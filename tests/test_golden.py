@@ -70,7 +70,8 @@ def test_cuda_path_matches_golden_vectors(talos):
     L.talos_rope(ctx.handle, P(xr), P(yr), P(c), P(s), 64, 10, 3, 1, 8, 0, 1, 0); ctx.synchronize(); assert rel_err(yr, G["rope_head_bwd"]) <= 1e-6
     # softmax / attention
     sx, sg = dev(G["sm_x"]), dev(G["sm_g"]); sy = e(11, 20); sdx = e(11, 20)
-    L.talos_softmax_fwd(ctx.handle, P(sx), P(sy), 11, 20, 1.0, 0); L.talos_softmax_bwd(ctx.handle, P(dev(G["sm_y"])), P(sg), P(sdx), 11, 20, 1.0, 0)
+    sy_ref = dev(G["sm_y"])
+    L.talos_softmax_fwd(ctx.handle, P(sx), P(sy), 11, 20, 1.0, 0); L.talos_softmax_bwd(ctx.handle, P(sy_ref), P(sg), P(sdx), 11, 20, 1.0, 0)
     ctx.synchronize(); assert rel_err(sy, G["sm_y"]) <= 2e-6 and rel_err(sdx, G["sm_dx"]) <= 1e-5
     q, k, v, go = dev(G["att_q"]), dev(G["att_k"]), dev(G["att_v"]), dev(G["att_go"]); O = torch.empty_like(v); Pr = torch.empty(3, 10, 10, device="cuda:0")
     dq = torch.empty_like(q); dk = torch.empty_like(k); dv = torch.empty_like(v); sc = 1.0 / math.sqrt(12.0)
@@ -82,13 +83,15 @@ def test_cuda_path_matches_golden_vectors(talos):
     # PPO loss and Adam
     n, A = 50, 5
     dl = e(n, A); dvv = e(n); st = torch.zeros(4, device="cuda:0")
-    L.talos_ppo_loss_fwd_bwd(ctx.handle, P(dev(G["ppo_logits"])), A, P(dev(G["ppo_values"])), 1, P(dev(G["ppo_actions"])), P(dev(G["ppo_old"])), P(dev(G["ppo_adv"])),
-                             P(dev(G["ppo_ret"])), n, A, 0.2, 0.5, 0.01, float(n), P(dl), A, P(dvv), 1, P(st))
+    t_ = {k: dev(G["ppo_" + k]) for k in ("logits", "values", "actions", "old", "adv", "ret")}      # keep every input alive for the call
+    L.talos_ppo_loss_fwd_bwd(ctx.handle, P(t_["logits"]), A, P(t_["values"]), 1, P(t_["actions"]), P(t_["old"]), P(t_["adv"]),
+                             P(t_["ret"]), n, A, 0.2, 0.5, 0.01, float(n), P(dl), A, P(dvv), 1, P(st))
     ctx.synchronize()
     assert rel_err(dl, G["ppo_dlogits"]) <= 1e-5 and rel_err(dvv, G["ppo_dvalues"]) <= 1e-5
     assert abs(host(st)[0] / n - float(G["ppo_loss"])) <= 1e-5 and abs(host(st)[1] - float(G["ppo_kl"])) <= 1e-4
     p = dev(G["adam_p0"]); m = torch.zeros(64, device="cuda:0"); vv = torch.zeros(64, device="cuda:0")
     for t in range(1, 4):
-        L.talos_adam_step(ctx.handle, P(p), P(dev(orc.f32r(G["adam_g"] * t))), P(m), P(vv), 64, t, 3e-4, 0.9, 0.999, 1e-8, 1.0, 0.0)
+        gt = dev(orc.f32r(G["adam_g"] * t))
+        L.talos_adam_step(ctx.handle, P(p), P(gt), P(m), P(vv), 64, t, 3e-4, 0.9, 0.999, 1e-8, 1.0, 0.0)
     ctx.synchronize(); assert rel_err(p, G["adam_p3"]) <= 1e-6
     ctx.close()
