@@ -189,10 +189,13 @@ struct TcArgs {
 
 // Shared storage layout (dynamic, 1024-byte aligned):
 //   [STAGES][A tile (hi)] [STAGES][B tile (hi)] ([STAGES][A lo] [STAGES][B lo] in X3 mode) barriers...
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(X3 ? 448 : 320, 1)
+// BPS (3xTF32 only): the B operand arrives already split into TF32 hi / lo matrices (two tensor maps), so the
+// converter warps only split A.  Used when B is small (weights): it is then split once per call instead of once
+// per output tile.
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false>
+__global__ void __launch_bounds__(X3 ? 448 : 320, MINB)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_c, TcArgs g) {
+               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, TcArgs g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
   extern __shared__ uint8_t smem_raw[];
@@ -230,15 +233,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b);
+      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); if (BPS) prefetch_tmap(&tmap_b_lo);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
         const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty + stage, phase ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full + stage, A_BYTES + B_BYTES);
+          mbar_expect_tx(full + stage, A_BYTES + B_BYTES + (BPS ? B_BYTES : 0));
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
+          if (BPS) {
+            uint8_t* bl_dst = sBlo + stage * B_BYTES;
+            if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_2d(bl_dst + j * (BK * 128), &tmap_b_lo, nb * BN + 32 * j, kb * BK, full + stage); }
+            else tma_load_2d(bl_dst, &tmap_b_lo, kb * BK, nb * BN, full + stage);
+          }
           if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, mb * BM + 32 * j, kb * BK, full + stage); }
           else tma_load_2d(a_dst, &tmap_a, kb * BK, mb * BM, full + stage);
           if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, nb * BN + 32 * j, kb * BK, full + stage); }
@@ -383,7 +391,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // The split is elementwise, so it is oblivious to the swizzle: same offset in, same offset out.
         float4* ahi = (float4*)(sA + stage * A_BYTES); float4* alo = (float4*)(sAlo + stage * A_BYTES);
         float4* bhi = (float4*)(sB + stage * B_BYTES); float4* blo = (float4*)(sBlo + stage * B_BYTES);
-        constexpr int CONV_ITERS = (A_BYTES + B_BYTES) / 16 / 128;
+        constexpr int CONV_ITERS = (A_BYTES + (BPS ? 0 : B_BYTES)) / 16 / 128;
 #pragma unroll 8
         for (int ci = 0; ci < CONV_ITERS; ++ci) {
           const int i = ct + ci * 128;
@@ -425,6 +433,17 @@ __global__ void round_tf32_kernel(const float* __restrict__ in, long long ld, in
   if (idx >= (long long)rows * out_ld) return;
   int r = (int)(idx / out_ld), c = (int)(idx % out_ld);
   out[idx] = c < cols ? __uint_as_float(cvt_tf32(in[(long long)r * ld + c])) : 0.f;
+}
+
+// Dense TF32 hi / lo copies of a [rows][cols] matrix: hi = rna(a), lo = rna(a - hi).
+__global__ void split_tf32_kernel(const float* __restrict__ in, long long ld, int rows, int cols, int out_ld, float* __restrict__ hi,
+                                  float* __restrict__ lo) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)rows * out_ld) return;
+  int r = (int)(idx / out_ld), c = (int)(idx % out_ld);
+  float a = c < cols ? in[(long long)r * ld + c] : 0.f;
+  float h = __uint_as_float(cvt_tf32(a));
+  hi[idx] = h; lo[idx] = __uint_as_float(cvt_tf32(a - h));
 }
 
 // ------------------------------------------------------------------ host side
@@ -475,28 +494,33 @@ size_t tc_smem_bytes() {
   return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + 8 * 32 * 32 * 4 + (3 * STAGES + 4) * 8 + 16 + 1024;
 }
 
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN>
-void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcArgs& g, int grid) {
-  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN>;
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false>
+void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tbl, const TcArgs& g, int grid) {
+  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS>;
   size_t smem = tc_smem_bytes<BN, STAGES, X3>();
   TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, X3 ? 448 : 320, smem, ctx->stream>>>(ta, tb, tc, g);
+  kern<<<grid, X3 ? 448 : 320, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
   talos_launched(ctx, "gemm_tcgen05");
 }
 
-template <int BN, int STAGES, bool X3>
-void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcArgs& g, int grid) {
-  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false>(ctx, ta, tb, tc, g, grid);
-  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true>(ctx, ta, tb, tc, g, grid);
-  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false>(ctx, ta, tb, tc, g, grid);
-  else launch_one<BN, STAGES, X3, true, true>(ctx, ta, tb, tc, g, grid);
+template <int BN, int STAGES, bool X3, int MINB = 1, bool BPS = false>
+void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tbl,
+                  const TcArgs& g, int grid) {
+  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
+  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
+  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
+  else launch_one<BN, STAGES, X3, true, true, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
 }
 
 void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
                int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
   int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
-  if (x3 && bn == 256 && getenv("TALOS_X3_BN128")) bn = 128;
+  // Short reductions over tall outputs are bound by the epilogue, not the main loop: 128-wide tiles with a
+  // two-stage pipeline fit two CTAs per SM (2 x 97 KB shared memory, 2 x 256 TMEM columns), which doubles
+  // the epilogue warps per SM.
+  const bool skinny = !x3 && N > 64 && K <= 512 && M >= 128LL * 2 * ctx->sm_count && getenv("TALOS_TC_SKINNY") != nullptr;
+  if (skinny) bn = 128;
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.m_tiles = (int)ceil_div(M, BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
@@ -519,9 +543,18 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   const bool round_a = !x3 && a_elems <= b_elems && a_elems <= (1 << 20), round_b = !x3 && !round_a && b_elems <= (1 << 20);
   const int64_t r_rows = round_a ? a_rows : b_rows, r_cols = round_a ? a_cols : b_cols, r_ld = (r_cols + 3) & ~int64_t(3);
   const size_t partial_bytes = splits > 1 ? ((sizeof(float) * (size_t)splits * M * N + 255) & ~size_t(255)) : 0;
-  const size_t round_bytes = (round_a || round_b) ? sizeof(float) * (size_t)(r_rows * r_ld) : 0;
+  const bool presplit = x3 && b_elems <= (1 << 20);
+  const int64_t s_ld = (b_cols + 3) & ~int64_t(3);
+  const size_t round_bytes = (round_a || round_b) ? sizeof(float) * (size_t)(r_rows * r_ld) : presplit ? 2 * sizeof(float) * (size_t)(b_rows * s_ld) : 0;
   char* scratch = (partial_bytes + round_bytes) ? (char*)talos_workspace(ctx, partial_bytes + round_bytes) : nullptr;
   if (splits > 1) g.partial = (float*)scratch;
+  const float* B_lo = nullptr;
+  if (presplit) {
+    float* hi = (float*)(scratch + partial_bytes); float* lo = hi + b_rows * s_ld;
+    split_tf32_kernel<<<(unsigned)ceil_div(b_rows * s_ld, 256), 256, 0, ctx->stream>>>(B, ldb, (int)b_rows, (int)b_cols, (int)s_ld, hi, lo);
+    talos_launched(ctx, "split_tf32");
+    B = hi; B_lo = lo; ldb = s_ld;
+  }
   if (round_a || round_b) {
     float* dst = (float*)(scratch + partial_bytes);
     round_tf32_kernel<<<(unsigned)ceil_div(r_rows * r_ld, 256), 256, 0, ctx->stream>>>(round_a ? A : B, round_a ? lda : ldb, (int)r_rows, (int)r_cols, (int)r_ld, dst);
@@ -532,6 +565,8 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   CUtensorMap ta, tb;
   bool ok = a_mn ? make_tmap(&ta, A, K, M, lda, BK, true) : make_tmap(&ta, A, M, K, lda, BM, false);
   ok = ok && (b_mn ? make_tmap(&tb, B, K, N, ldb, BK, true) : make_tmap(&tb, B, N, K, ldb, bn, false));
+  CUtensorMap tbl = tb;
+  if (presplit) ok = ok && (b_mn ? make_tmap(&tbl, B_lo, K, N, ldb, BK, true) : make_tmap(&tbl, B_lo, N, K, ldb, bn, false));
   // Results leave through TMA stores when the destination is 16-byte aligned with a 16-byte pitch, N is a
   // multiple of 4 (a TMA store clips the innermost axis in 16-byte units, so a ragged N would spill into the
   // pitch padding) and the epilogue does not also save the pre-activation; otherwise through direct stores.
@@ -542,8 +577,14 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   if (splits > 1) { if (!(N & 3)) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, g.partial, splits, M, N, N); } }
   else if (!(((uintptr_t)C) & 15) && !(ldc & 3) && !(N & 3) && !epi.aux_out && !both && epi_aligned) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, C, 1, M, N, ldc); }
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
-  int grid = std::min(tiles * splits, ctx->sm_count);
-#define TALOS_TC_CASE(BNv, ST, ST3) if (bn == BNv) { if (x3) launch_major<BNv, ST3, true>(ctx, a_mn, b_mn, ta, tb, tc, g, grid); else launch_major<BNv, ST, false>(ctx, a_mn, b_mn, ta, tb, tc, g, grid); }
+  int grid = std::min(tiles * splits, ctx->sm_count * (skinny ? 2 : 1));
+  if (skinny) { launch_major<128, 2, false, 2>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid); return; }
+#define TALOS_TC_CASE(BNv, ST, ST3)                                                                          \
+  if (bn == BNv) {                                                                                           \
+    if (x3 && presplit) launch_major<BNv, ST3, true, 1, true>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);    \
+    else if (x3) launch_major<BNv, ST3, true>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                     \
+    else launch_major<BNv, ST, false>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                             \
+  }
   TALOS_TC_CASE(256, 4, 2) else TALOS_TC_CASE(128, 6, 3) else TALOS_TC_CASE(64, 8, 4) else TALOS_TC_CASE(32, 8, 4)
 #undef TALOS_TC_CASE
   if (splits > 1) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
