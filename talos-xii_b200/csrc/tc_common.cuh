@@ -1,0 +1,250 @@
+// Device-side building blocks shared by the tensor-core GEMM kernels: PTX wrappers (mbarrier, TMA, tcgen05,
+// TMEM), shared-memory matrix descriptors, the fused epilogue helpers and the kernel argument block.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+// Kernel argument block of the tensor-core GEMM kernels (shared by the one-CTA and CTA-pair launchers).
+struct TcArgs {
+  int M, N, K;
+  int m_tiles, n_tiles, splits, kb_total, kb_per_split;
+  float* C; long long ldc;
+  float* partial;                          // [splits][M][N] when splits > 1
+  EpiArgs epi;
+  int32_t* status;
+  int tma_out;                             // 1: results leave through TMA stores (tmap_c), 0: direct stores
+};
+
+namespace {
+
+constexpr int BM = 128;                 // tile rows = TMEM lanes
+constexpr int BK = 32;                  // fp32 per 128-byte swizzle row
+constexpr int UMMA_K = 8;               // K per tcgen05.mma.kind::tf32
+constexpr uint32_t WAIT_SPINS = 1u << 22;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after raising *abort_flag) when the barrier never flips or when
+// another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) { if (*abort_flag) return false; __nanosleep(i > 4096 ? 256 : 32); }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N_PENDING>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N_PENDING) : "memory"); }
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cvt_tf32(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return r; }
+
+// Shared-memory matrix descriptor for a swizzled operand tile (1024-byte aligned).
+//  K-major : layout 2 (128B swizzle, 16-byte atoms): rows of 128 B, 8-row groups 1024 B apart (SBO);
+//            the leading offset is unused (1).
+//  MN-major: fp32 operands must use layout 1 (128B swizzle with 32-byte atoms, 4-row period):
+//            32-float column chunks, each [BK rows][128 B]; chunk stride (LBO) = BK*128 B,
+//            4-row k-groups 512 B apart (SBO).  TMA writes it with SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;                  // descriptor version for this architecture
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+
+// Epilogue over one transposed 32x32 staging tile: lane = column, loop over rows.  The activation
+// and derivative kinds are template parameters so the row loop carries no per-element branches.
+template <int ACT, int DACT>
+__device__ __forceinline__ void epilogue_rows_t(const EpiArgs& e, const float* stage, int lane, long long m0, int rows_valid,
+                                                long long n, bool col_ok, float* C, long long ldc) {
+  const float bias_v = (e.bias && col_ok) ? __ldg(e.bias + n) : 0.f;
+#pragma unroll 4
+  for (int rr = 0; rr < rows_valid; ++rr) {
+    if (!col_ok) continue;
+    const long long m = m0 + rr;
+    float v = stage[rr * 32 + (lane ^ rr)] + bias_v;
+    if (e.aux_out) e.aux_out[m * e.ld_aux_out + n] = v;
+    if (ACT) v = talos_act(v, ACT);
+    if (DACT) v *= talos_dact(__ldg(e.aux_in + m * e.ld_aux_in + n), DACT);
+    if (e.beta) v += C[m * ldc + n];
+    C[m * ldc + n] = v;
+  }
+}
+__device__ __noinline__ void epilogue_rows(const EpiArgs& e, const float* stage, int lane, long long m0, int rows_valid, long long n,
+                                           bool col_ok, float* C, long long ldc) {
+  const int dact = e.aux_in ? e.dact : 0;
+  switch (e.act * 4 + dact) {
+#define TALOS_EPI_CASE(A, D) case (A) * 4 + (D): epilogue_rows_t<A, D>(e, stage, lane, m0, rows_valid, n, col_ok, C, ldc); break;
+    TALOS_EPI_CASE(0, 0) TALOS_EPI_CASE(0, 1) TALOS_EPI_CASE(0, 2) TALOS_EPI_CASE(0, 3)
+    TALOS_EPI_CASE(1, 0) TALOS_EPI_CASE(1, 1) TALOS_EPI_CASE(1, 2) TALOS_EPI_CASE(1, 3)
+    TALOS_EPI_CASE(2, 0) TALOS_EPI_CASE(2, 1) TALOS_EPI_CASE(2, 2) TALOS_EPI_CASE(2, 3)
+    TALOS_EPI_CASE(3, 0) TALOS_EPI_CASE(3, 1) TALOS_EPI_CASE(3, 2) TALOS_EPI_CASE(3, 3)
+#undef TALOS_EPI_CASE
+    default: break;
+  }
+}
+
+// Fused epilogue on one group of four consecutive columns of one accumulator row.  Everything is a
+// named scalar or a float4 (no arrays), so the accumulator values never leave registers.  The host
+// guarantees 16-byte alignment of every operand on this path.
+template <int ACT, int DACT>
+__device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restrict__ bias, const float* __restrict__ aux_in,
+                                                 const float* __restrict__ c_old) {
+  if (bias) { const float4 b = __ldg((const float4*)bias); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+  if (ACT) { v.x = talos_act(v.x, ACT); v.y = talos_act(v.y, ACT); v.z = talos_act(v.z, ACT); v.w = talos_act(v.w, ACT); }
+  if (DACT) {
+    const float4 a = __ldg((const float4*)aux_in);
+    v.x *= talos_dact(a.x, DACT); v.y *= talos_dact(a.y, DACT); v.z *= talos_dact(a.z, DACT); v.w *= talos_dact(a.w, DACT);
+  }
+  if (c_old) { const float4 o = *(const float4*)c_old; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+  return v;
+}
+
+
+
+// One epilogue warp's share of a finished 128 x BN accumulator: warp w (2..9) owns TMEM lane quadrant w%4 (32 rows,
+// one per lane) and half of the columns, drained 32 columns at a time.  `t_base` is the TMEM address of the
+// accumulator's first column, `m_base` the global row of TMEM lane 0, `stage` this warp's 4 KB staging buffer.
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensorMap* tmap_c, uint32_t t_base, int warp, int lane, float* stage,
+                                                 long long m_base, int nb, int ks, uint32_t& store_count) {
+  // Each warp drains its 32-lane quadrant (one accumulator row per lane) 32 columns at a time.
+  const int quad = warp & 3, half = (warp - 2) >> 2;
+  const long long m0 = m_base + quad * 32;
+  const uint32_t t_row = t_base + ((uint32_t)(quad * 32) << 16);
+  const int rows_valid = (int)min((long long)32, (long long)g.M - m0);
+  constexpr int HALF_COLS = BN >= 64 ? BN / 2 : BN;
+#pragma unroll 1
+  for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 32) {
+    const long long n0 = (long long)nb * BN + c0;
+    if (n0 >= g.N || rows_valid <= 0) break;               // uniform across the warp
+    uint32_t r[32];
+    tmem_ld32(t_row + (uint32_t)c0, r);
+    tmem_ld_wait();
+    if (g.tma_out) {
+      // Fused epilogue in registers, then a 128B-swizzled 32x32 tile in shared memory that one
+      // lane hands to the TMA store engine (clipped to [M,N] by the tensor map).
+      float* buf = stage;
+      if (store_count >= 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+      {
+        const bool fuse = (g.splits == 1) && (lane < rows_valid);
+        const long long m = m0 + lane;
+        const int dact = g.epi.aux_in ? g.epi.dact : 0;
+        const float* bias_p = (fuse && g.epi.bias) ? g.epi.bias + n0 : nullptr;
+        const float* aux_p = (fuse && dact) ? g.epi.aux_in + m * g.epi.ld_aux_in + n0 : nullptr;
+        const float* cold_p = (fuse && g.epi.beta) ? g.C + m * g.ldc + n0 : nullptr;
+        const int groups = (int)min((long long)8, (g.N - n0) >> 2);     // N is a multiple of 4 on this path
+#define TALOS_EPI_STORE(A, D)                                                                                           \
+  _Pragma("unroll") for (int c = 0; c < 8; ++c) {                                                                      \
+float4 v = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),    \
+                       __uint_as_float(r[4 * c + 3]));                                                             \
+if (fuse && c < groups)                                                                                             \
+  v = epilogue_group<A, D>(v, bias_p ? bias_p + 4 * c : nullptr, aux_p ? aux_p + 4 * c : nullptr,                  \
+                           cold_p ? cold_p + 4 * c : nullptr);                                                      \
+*(float4*)(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) = v;                                                          \
+  }
+        switch (fuse ? g.epi.act * 4 + dact : 0) {
+          case 1: TALOS_EPI_STORE(0, 1) break;
+          case 2: TALOS_EPI_STORE(0, 2) break;
+          case 3: TALOS_EPI_STORE(0, 3) break;
+          case 4: TALOS_EPI_STORE(1, 0) break;
+          case 8: TALOS_EPI_STORE(2, 0) break;
+          case 12: TALOS_EPI_STORE(3, 0) break;
+          default: TALOS_EPI_STORE(0, 0) break;
+        }
+#undef TALOS_EPI_STORE
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { tma_store_3d(tmap_c, buf, (int)n0, (int)m0, ks); tma_store_commit(); }
+      ++store_count;
+    } else {
+      // Unaligned output: transpose through a padded tile so lanes run along the contiguous axis.
+#pragma unroll
+      for (int j = 0; j < 32; ++j) stage[lane * 32 + (j ^ lane)] = __uint_as_float(r[j]);    // XOR-swizzled transpose tile
+      __syncwarp();
+      const long long n = n0 + lane;
+      const bool col_ok = n < g.N;
+      if (g.splits > 1) {
+        float* P = g.partial + ((long long)ks * g.M + m0) * g.N + n;
+#pragma unroll 4
+        for (int rr = 0; rr < rows_valid; ++rr) if (col_ok) P[(long long)rr * g.N] = stage[rr * 32 + (lane ^ rr)];
+      } else {
+        epilogue_rows(g.epi, stage, lane, m0, rows_valid, n, col_ok, g.C, g.ldc);
+      }
+      __syncwarp();
+    }
+  }
+}
+
+}  // namespace
