@@ -285,6 +285,8 @@ void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, c
   else launch_one<BN, STAGES, X3, true, true, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
 }
 
+thread_local bool g_check_pair = false;   // set by the start-up self-check so that its short reduction still exercises the pair kernel
+
 void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
                int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
@@ -296,8 +298,11 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   if (skinny) bn = 128;   // (takes precedence over the CTA-pair kernel, which needs bn == 256)
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
-  // 256-wide outputs with at least 256 rows run on CTA pairs (cta_group::2): 256 x 256 tiles.
-  const bool pair = bn == 256 && M >= 256 && !getenv("TALOS_TC_NO_PAIR");
+  // 256-wide outputs with at least 256 rows and a long reduction run on CTA pairs (cta_group::2): 256 x 256 tiles
+  // halve the operand bytes each SM has to pull per flop.  For short reductions (K = 256: 8 k-blocks a tile) the
+  // pair's start-up and cross-CTA hand-offs cost more than that saves (measured 8 % slower at K = 256, 10 % faster
+  // at K = 2048), so those stay on the one-CTA kernel.
+  const bool pair = bn == 256 && M >= 256 && (K >= 1024 || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
   g.m_tiles = (int)ceil_div(M, pair ? 2 * BM : BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
   int tiles = g.m_tiles * g.n_tiles, splits = 1;
   const int workers = pair ? ctx->sm_count / 2 : ctx->sm_count;   // CTAs, or CTA pairs
@@ -419,7 +424,13 @@ bool self_check_shape(talos_ctx* ctx, const int M) {
 }
 
 // Rows 200: one-CTA kernels; rows 456: the CTA-pair kernel (two 256-row tiles, the second one ragged).
-bool self_check(talos_ctx* ctx) { return self_check_shape(ctx, 200) && self_check_shape(ctx, 456); }
+bool self_check(talos_ctx* ctx) {
+  bool ok = self_check_shape(ctx, 200);
+  g_check_pair = true;
+  ok = ok && self_check_shape(ctx, 456);
+  g_check_pair = false;
+  return ok;
+}
 
 }  // namespace
 

@@ -49,7 +49,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) { if (*abort_flag) return false; __nanosleep(i > 4096 ? 256 : 32); }
+    // try_wait itself parks the thread for a hardware-defined interval, so the loop is not hot; back off with
+    // nanosleep only when the wait is clearly long (the epilogue waiting out a whole main loop, or a stall).
+    if (i > 64 && (i & 63) == 0) { if (*abort_flag) return false; if (i > (1u << 14)) __nanosleep(128); }
   }
   *abort_flag = 1;
   return false;
@@ -103,7 +105,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ uint32_t cvt_tf32(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return r; }
+// Round to TF32 (10 mantissa bits), nearest with ties away from zero -- the semantics of cvt.rna.tf32.f32 -- with two
+// integer operations on the bit pattern (add half an ulp of the kept part to the magnitude, clear the 13 dropped
+// bits); the conversion instruction itself issues at a fraction of the integer rate and was the converter warps'
+// bottleneck.  A carry out of the mantissa correctly bumps the exponent; Inf/NaN inputs are not expected here.
+__device__ __forceinline__ uint32_t cvt_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u; }
 
 // Shared-memory matrix descriptor for a swizzled operand tile (1024-byte aligned).
 //  K-major : layout 2 (128B swizzle, 16-byte atoms): rows of 128 B, 8-row groups 1024 B apart (SBO);

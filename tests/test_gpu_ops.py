@@ -85,7 +85,7 @@ def test_gemm_odd_shapes_all_ops(talos, ctx, mode):
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
 def test_gemm_aligned_rect_shapes(talos, ctx, mode):
-    for (M, N, K) in [(256, 128, 64), (384, 256, 96), (1024, 16, 256), (128, 512, 1024), (4096, 256, 64), (640, 320, 200), (256, 1152, 1024)]:  # the last one has a B operand too large for the pre-split / pre-round path
+    for (M, N, K) in [(256, 128, 64), (384, 256, 96), (1024, 16, 256), (128, 512, 1024), (4096, 256, 64), (640, 320, 200), (600, 512, 1056), (256, 1152, 1024)]:  # the last one has a B operand too large for the pre-split / pre-round path
         for opA, opB in [(0, 0), (0, 1), (1, 0), (1, 1)]:
             A = normal(M + K, (K, M) if opA else (M, K)); B = normal(N + K + 1, (N, K) if opB else (K, N))
             got = gemm(talos, ctx, opA, opB, A, B, mode)
