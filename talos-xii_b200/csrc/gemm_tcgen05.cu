@@ -302,7 +302,10 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // halve the operand bytes each SM has to pull per flop.  For short reductions (K = 256: 8 k-blocks a tile) the
   // pair's start-up and cross-CTA hand-offs cost more than that saves (measured 8 % slower at K = 256, 10 % faster
   // at K = 2048), so those stay on the one-CTA kernel.
-  const bool pair = bn == 256 && M >= 256 && (K >= 1024 || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
+  // They also need enough 256 x 256 tiles to occupy every CTA pair without splitting K (the split-K weight-gradient
+  // shapes have one or two tiles and are faster on 148 independent CTAs than on 74 pairs).
+  const bool pair_shape = K >= 1024 && ceil_div(M, 2 * BM) * ceil_div(N, 256) >= ctx->sm_count / 2;
+  const bool pair = bn == 256 && M >= 256 && (pair_shape || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
   g.m_tiles = (int)ceil_div(M, pair ? 2 * BM : BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
   int tiles = g.m_tiles * g.n_tiles, splits = 1;
   const int workers = pair ? ctx->sm_count / 2 : ctx->sm_count;   // CTAs, or CTA pairs
