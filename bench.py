@@ -104,9 +104,10 @@ def init_params(talos):
     return p
 
 
-def cpu_baseline(sample=8192, threads=None):
-    """The oracle (CPU restatement of the reference's algorithm, f64, row-parallel like Rayon) on a bounded
-    sample of the same workload: `sample` transitions, one epoch, one minibatch."""
+def cpu_baseline(sample=MB, steps=12, budget_s=25.0, threads=None):
+    """The oracle (CPU restatement of the reference's algorithm, f64, row-parallel like Rayon) on a bounded sample of
+    the same workload: up to `steps` optimizer steps of `sample` transitions each (one minibatch per step), stopping
+    early once `budget_s` seconds of CPU time are spent.  Returns (samples/s, threads, seconds, steps done)."""
     import numpy as np
     import oracle as orc
     from oracle import model as om
@@ -120,30 +121,32 @@ def cpu_baseline(sample=8192, threads=None):
     model = om.MlpActorCritic(params)
     old = model.log_prob(obs, act, threads)
     om.ppo_update(model, obs[:1024], act[:1024], old[:1024], adv[:1024], ret[:1024], 1, 1024, threads=threads)   # warm-up
-    t0 = time.perf_counter()
-    om.ppo_update(model, obs, act, old, adv, ret, 1, sample, threads=threads)
+    done = 0; t0 = time.perf_counter()
+    while done < steps:
+        om.ppo_update(model, obs, act, old, adv, ret, 1, sample, threads=threads)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
     dt = time.perf_counter() - t0
-    return sample / dt, threads, dt
+    return sample * done / dt, threads, dt, done
 
 
 def run_reference(args):
+    """The reference's own CPU implementation of the path, timed on the host cores.  The Rust crate cannot be built in
+    this image (no cargo / rustc), so this is the oracle port with all host threads; a step is one optimizer step on
+    one 65 536-transition minibatch, the same unit as the GPU arm's step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 8192
-    steps = max(1, args.steps)
-    vals = []
-    for _ in range(min(args.warmup, 1)):
-        cpu_baseline(2048)
-    t_all = 0.0
-    for _ in range(min(steps, 8)):       # each step a bounded sample of the workload; capped so the run ends within minutes
-        v, threads, dt = cpu_baseline(sample); vals.append(v); t_all += dt
-    value = sample * len(vals) / t_all
-    out = {"impl": "reference", "metric": "ppo_update_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": len(vals),
-           "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t_all / len(vals), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "f64", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": "%d transitions per step, one minibatch, one epoch" % sample},
+    warm = min(args.warmup, 1)
+    if warm:
+        cpu_baseline(8192, 1)
+    value, threads, dt, done = cpu_baseline(MB, max(1, min(args.steps, 64)), budget_s=150.0)
+    out = {"impl": "reference", "metric": "ppo_update_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": done,
+           "warmup": warm, "ms_per_step": 1e3 * dt / done, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "f64", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": "%d transitions per step (one minibatch), %d steps" % (MB, done)},
            "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
-                            "sample": "%d steps x %d transitions through the oracle (C f64 restatement, %d threads)" % (len(vals), sample, threads)},
+                            "sample": "%d steps x %d transitions through the oracle (C f64 restatement of the reference, %d threads, %.1f s)" % (done, MB, threads, dt)},
            "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(out), flush=True)
 
@@ -285,9 +288,9 @@ def run_ours(args):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        v, threads, dt = cpu_baseline(8192)
+        v, threads, dt, done = cpu_baseline(MB, 16, budget_s=12.0)
         cpu = {"value": v, "unit": "samples/s", "cores": threads, "kind": "port",
-               "sample": "8192 transitions, one epoch, one minibatch through the oracle (C f64 restatement of the reference, %d threads, %.1f s)" % (threads, dt)}
+               "sample": "%d optimizer steps x %d transitions through the oracle (C f64 restatement of the reference, %d threads, %.1f s)" % (done, MB, threads, dt)}
 
     if rank == 0:
         out = {"metric": "ppo_update_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
