@@ -173,17 +173,20 @@ talos_status talos_softmax_fwd(talos_ctx* ctx, const float* x, float* y, int64_t
 talos_status talos_softmax_bwd(talos_ctx* ctx, const float* y, const float* dy, float* dx, int64_t rows,
                                int64_t len, float scale, int32_t accumulate);
 
-/* ---- attention core: scores -> scale -> softmax -> .V without writing scores to HBM -------- */
+/* ---- attention core: scores -> scale -> softmax -> .V ---------------------------------------- */
 /* q,k [BH,S,dqk], v [BH,S,dv], out [BH,S,dv]; probs (nullable) [BH,S,S] is written when the tape
  * needs it.  Replaces batched_matmul_qt_k + scale_tensor + softmax + batched_matmul_probs_v
- * (src/transformer.rs:539-550).  S <= 128. */
+ * (src/transformer.rs:539-550).  mode FP32: one fused CUDA-core kernel, scores never leave the SM,
+ * S <= 128.  mode TF32 / TF32X3: two batched tensor-core GEMMs around an in-place softmax (S <= 1024);
+ * shapes the tensor-core GEMM does not take fall back to the fused kernel. */
 talos_status talos_attention_fwd(talos_ctx* ctx, const float* q, const float* k, const float* v, float* out,
                                  float* probs, int64_t BH, int64_t S, int64_t dqk, int64_t dv, float scale,
-                                 int32_t causal);
-/* Backward from saved probs: dq,dk,dv are overwritten. */
+                                 int32_t causal, int32_t mode);
+/* Backward from saved probs (the closures at src/transformer.rs:920-955, :1010-1046, :1063-1068,
+ * :1098-1117): dq,dk,dv are overwritten.  The four products run as batched GEMMs in `mode`. */
 talos_status talos_attention_bwd(talos_ctx* ctx, const float* q, const float* k, const float* v,
                                  const float* probs, const float* dout, float* dq, float* dk, float* dv,
-                                 int64_t BH, int64_t S, int64_t dqk, int64_t dvdim, float scale);
+                                 int64_t BH, int64_t S, int64_t dqk, int64_t dvdim, float scale, int32_t mode);
 
 /* ---- layout ops --------------------------------------------------------------------------- */
 /* Tensor::transpose (src/autograd.rs:632-739): swap two axes of a rank<=6 tensor (full copy).

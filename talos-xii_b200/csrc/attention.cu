@@ -128,14 +128,34 @@ void talos_attention_launch(talos_ctx* ctx, HeadView q1, HeadView q2, HeadView k
   talos_launched(ctx, "attention_fwd");
 }
 
+// Tensor-core route of the forward pass (TF32 / 3xTF32 modes): scores = Q.K^T as one batched tensor-core GEMM written
+// to `sc` (the caller's probs buffer, or scratch), softmax in place, out = P.V as a second batched GEMM.  The scores
+// make one round trip through HBM (~4 S^2 x 4 bytes per head), which at S = 128 still costs a tenth of the fused
+// CUDA-core kernel's arithmetic time.  Returns false when the tensor-core GEMM does not take the shape.
+static bool attention_fwd_tc(talos_ctx* ctx, const float* q, const float* k, const float* v, float* out, float* probs,
+                             int64_t BH, int64_t S, int64_t dqk, int64_t dv, float scale, int causal, int mode) {
+  if (S > 1024) return false;                                       // row softmax limit
+  float* sc = probs ? probs : (float*)talos_workspace2(ctx, sizeof(float) * (size_t)(BH * S * S));
+  const EpiArgs none = talos_epi_args(nullptr);
+  if (!talos_gemm_tc_launch_batched(ctx, TALOS_OP_N, TALOS_OP_T, S, S, dqk, q, dqk, S * dqk, k, dqk, S * dqk, sc, S, S * S, BH, mode, none))
+    return false;
+  talos_status st = talos_softmax_fwd(ctx, sc, sc, BH * S, S, scale, causal ? S : 0);
+  if (st != TALOS_OK) throw talos_error(st, talos_last_error_string());
+  st = talos_gemm_batched(ctx, TALOS_OP_N, TALOS_OP_N, S, dv, S, sc, S, S * S, v, dv, S * dv, out, dv, S * dv, BH, 0, mode);
+  if (st != TALOS_OK) throw talos_error(st, talos_last_error_string());
+  return true;
+}
+
 TALOS_API talos_status talos_attention_fwd(talos_ctx* ctx, const float* q, const float* k, const float* v, float* out,
                                            float* probs, int64_t BH, int64_t S, int64_t dqk, int64_t dv, float scale,
-                                           int32_t causal) {
+                                           int32_t causal, int32_t mode) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
   TALOS_REQUIRE(BH >= 0 && S >= 0 && dqk >= 1 && dv >= 1, TALOS_ERR_SHAPE, "bad attention shape");
+  TALOS_REQUIRE(mode >= TALOS_MODE_FP32 && mode <= TALOS_MODE_TF32, TALOS_ERR_ARG, "bad arithmetic mode");
   if (BH == 0 || S == 0) return TALOS_OK;
   TALOS_REQUIRE(q && k && v && out, TALOS_ERR_ARG, "null pointer");
+  if (mode != TALOS_MODE_FP32 && attention_fwd_tc(ctx, q, k, v, out, probs, BH, S, dqk, dv, scale, causal ? 1 : 0, mode)) return TALOS_OK;
   HeadView none{nullptr, 0, 0, 0, 0};
   talos_attention_launch(ctx, HeadView{q, S * dqk, 0, dqk, (int)dqk}, none, HeadView{k, S * dqk, 0, dqk, (int)dqk}, none,
                          HeadView{v, S * dv, 0, dv, (int)dv}, HeadViewOut{out, S * dv, 0, dv, (int)dv}, probs, BH, 1, (int)S,
@@ -146,25 +166,27 @@ TALOS_API talos_status talos_attention_fwd(talos_ctx* ctx, const float* q, const
 // Backward from the saved probabilities, as the product of the reference's four closures
 // (src/transformer.rs:1010-1046, :1098-1117, :1063-1068, :920-955):
 //   dV = P^T.dO ; dP = dO.V^T ; dS = scale * P * (dP - rowsum(dP*P)) ; dQ = dS.K ; dK = dS^T.Q
+// The four products are batched GEMMs in the requested arithmetic mode (tensor cores for TF32 / 3xTF32).
 TALOS_API talos_status talos_attention_bwd(talos_ctx* ctx, const float* q, const float* k, const float* v,
                                            const float* probs, const float* dout, float* dq, float* dk, float* dv,
-                                           int64_t BH, int64_t S, int64_t dqk, int64_t dvd, float scale) {
+                                           int64_t BH, int64_t S, int64_t dqk, int64_t dvd, float scale, int32_t mode) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
   TALOS_REQUIRE(BH >= 0 && S >= 0 && dqk >= 1 && dvd >= 1 && S <= 1024, TALOS_ERR_SHAPE, "bad attention shape");
+  TALOS_REQUIRE(mode >= TALOS_MODE_FP32 && mode <= TALOS_MODE_TF32, TALOS_ERR_ARG, "bad arithmetic mode");
   if (BH == 0 || S == 0) return TALOS_OK;
   TALOS_REQUIRE(q && k && v && probs && dout && dq && dk && dv, TALOS_ERR_ARG, "null pointer");
   float* dS = (float*)talos_workspace2(ctx, sizeof(float) * (size_t)(BH * S * S));
   talos_status st;
-  st = talos_gemm_batched(ctx, TALOS_OP_T, TALOS_OP_N, S, dvd, S, probs, S, S * S, dout, dvd, S * dvd, dv, dvd, S * dvd, BH, 0, TALOS_MODE_FP32);
+  st = talos_gemm_batched(ctx, TALOS_OP_T, TALOS_OP_N, S, dvd, S, probs, S, S * S, dout, dvd, S * dvd, dv, dvd, S * dvd, BH, 0, mode);
   if (st) return st;
-  st = talos_gemm_batched(ctx, TALOS_OP_N, TALOS_OP_T, S, S, dvd, dout, dvd, S * dvd, v, dvd, S * dvd, dS, S, S * S, BH, 0, TALOS_MODE_FP32);
+  st = talos_gemm_batched(ctx, TALOS_OP_N, TALOS_OP_T, S, S, dvd, dout, dvd, S * dvd, v, dvd, S * dvd, dS, S, S * S, BH, 0, mode);
   if (st) return st;
   st = talos_softmax_bwd(ctx, probs, dS, dS, BH * S, S, scale, 0);
   if (st) return st;
-  st = talos_gemm_batched(ctx, TALOS_OP_N, TALOS_OP_N, S, dqk, S, dS, S, S * S, k, dqk, S * dqk, dq, dqk, S * dqk, BH, 0, TALOS_MODE_FP32);
+  st = talos_gemm_batched(ctx, TALOS_OP_N, TALOS_OP_N, S, dqk, S, dS, S, S * S, k, dqk, S * dqk, dq, dqk, S * dqk, BH, 0, mode);
   if (st) return st;
-  st = talos_gemm_batched(ctx, TALOS_OP_T, TALOS_OP_N, S, dqk, S, dS, S, S * S, q, dqk, S * dqk, dk, dqk, S * dqk, BH, 0, TALOS_MODE_FP32);
+  st = talos_gemm_batched(ctx, TALOS_OP_T, TALOS_OP_N, S, dqk, S, dS, S, S * S, q, dqk, S * dqk, dk, dqk, S * dqk, BH, 0, mode);
   if (st) return st;
   TALOS_ENTRY_END
 }

@@ -134,4 +134,7 @@ void talos_gemm_fp32_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t
 bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A,
                           int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, int mode,
                           const EpiArgs& epi);
+bool talos_gemm_tc_launch_batched(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                                  int64_t strideA, const float* B, int64_t ldb, int64_t strideB, float* C, int64_t ldc, int64_t strideC,
+                                  int64_t batch, int mode, const EpiArgs& epi);
 void talos_gemm_tc_release(talos_ctx* ctx);

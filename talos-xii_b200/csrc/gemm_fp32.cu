@@ -248,6 +248,9 @@ TALOS_API talos_status talos_gemm_batched(talos_ctx* ctx, int32_t opA, int32_t o
   TALOS_REQUIRE(batch >= 0 && batch < 65536 * 16, TALOS_ERR_SHAPE, "bad batch count");
   if (M == 0 || N == 0 || batch == 0) return TALOS_OK;
   EpiArgs e = talos_epi_args(nullptr); e.beta = beta ? 1 : 0;
+  if (mode != TALOS_MODE_FP32 &&
+      talos_gemm_tc_launch_batched(ctx, opA, opB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, batch, mode, e))
+    return TALOS_OK;
   // grid.z is limited to 65535 slices per launch.
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
     int64_t nb = std::min<int64_t>(65535, batch - b0);

@@ -68,7 +68,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_mn = g.m_tiles * g.n_tiles;
-  const int items = tiles_mn * g.splits;
+  const int per_batch = tiles_mn * g.splits;              // work items of one batch member
+  const int items = per_batch * g.batch;
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -76,7 +77,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); if (BPS) prefetch_tmap(&tmap_b_lo);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-        const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+        const int bz = it / per_batch, r = it - bz * per_batch;
+        const int ks = r / tiles_mn, rem = r % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty + stage, phase ^ 1, abort_flag)) { ok = false; break; }
@@ -84,13 +86,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
           if (BPS) {
             uint8_t* bl_dst = sBlo + stage * B_BYTES;
-            if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_2d(bl_dst + j * (BK * 128), &tmap_b_lo, nb * BN + 32 * j, kb * BK, full + stage); }
-            else tma_load_2d(bl_dst, &tmap_b_lo, kb * BK, nb * BN, full + stage);
+            if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_3d(bl_dst + j * (BK * 128), &tmap_b_lo, nb * BN + 32 * j, kb * BK, bz, full + stage); }
+            else tma_load_3d(bl_dst, &tmap_b_lo, kb * BK, nb * BN, bz, full + stage);
           }
-          if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, mb * BM + 32 * j, kb * BK, full + stage); }
-          else tma_load_2d(a_dst, &tmap_a, kb * BK, mb * BM, full + stage);
-          if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, nb * BN + 32 * j, kb * BK, full + stage); }
-          else tma_load_2d(b_dst, &tmap_b, kb * BK, nb * BN, full + stage);
+          if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_3d(a_dst + j * (BK * 128), &tmap_a, mb * BM + 32 * j, kb * BK, bz, full + stage); }
+          else tma_load_3d(a_dst, &tmap_a, kb * BK, mb * BM, bz, full + stage);
+          if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_3d(b_dst + j * (BK * 128), &tmap_b, nb * BN + 32 * j, kb * BK, bz, full + stage); }
+          else tma_load_3d(b_dst, &tmap_b, kb * BK, nb * BN, bz, full + stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -105,7 +107,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024, a_lay = A_MN ? 1 : 2, b_lay = B_MN ? 1 : 2;
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-        const int ks = it / tiles_mn;
+        const int ks = (it % per_batch) / tiles_mn;
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
         if (!mbar_wait(tempty + acc, acc_phase[acc] ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -141,10 +143,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // taking half of the tile's columns.  The epilogue is latency-bound per warp, so it needs the extra warps.
     int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-      const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+      const int bz = it / per_batch, r = it - bz * per_batch;
+      const int ks = r / tiles_mn, rem = r % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
       if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
       tc_fence_after();
-      tc_epilogue_tile<BN>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32), (long long)mb * BM, nb, ks, store_count);
+      tc_epilogue_tile<BN>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32), (long long)mb * BM, nb, ks, bz, store_count);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + acc);
@@ -157,7 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int ct = threadIdx.x - 320;                          // 0..127
     int stage = 0; uint32_t phase = 0; bool ok = true;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
-      const int ks = it / tiles_mn;
+      const int ks = (it % per_batch) / tiles_mn;
       const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(full + stage, phase, abort_flag)) { ok = false; break; }
@@ -235,26 +238,31 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D fp32 tensor map over a row-major [rows][cols] matrix (cols contiguous), box = [box_rows][32 cols].
-bool make_tmap(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool mn_major) {
+// 3-D fp32 tensor map over `batch` row-major [rows][cols] matrices (cols contiguous) `stride` elements apart,
+// box = [1][box_rows][32 cols].  A plain GEMM is a batch of one.  Rows past the end of a batch member are filled
+// with zeros by the copy engine, never read from the next member.
+bool make_tmap(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool mn_major,
+               int64_t batch = 1, int64_t stride = 0) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-  cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  if (batch <= 1) { batch = 1; stride = rows * ld; }
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)stride * sizeof(float)};
+  cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
 // 3-D fp32 tensor map for results: [slabs][rows][cols], box = [1][32][32], 128B swizzle.  C itself is one
-// slab; split-K partial sums are `splits` dense slabs, clipped per slab by the map.
-bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t rows, int64_t cols, int64_t ld) {
+// slab; split-K partial sums are `splits` dense slabs; a batched product has one slab per batch member,
+// `slab_stride` elements apart.  Stores are clipped per slab by the map.
+bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t rows, int64_t cols, int64_t ld, int64_t slab_stride) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)slabs};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)ld * (cuuint64_t)rows * sizeof(float)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)slab_stride * sizeof(float)};
   cuuint32_t box[3] = {32u, 32u, 1u};
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -287,17 +295,22 @@ void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, c
 
 thread_local bool g_check_pair = false;   // set by the start-up self-check so that its short reduction still exercises the pair kernel
 
+// A batched product: `batch` independent GEMMs whose operands are `stride*` elements apart (batch 1: a plain GEMM).
+struct TcBatch { int64_t batch, stride_a, stride_b, stride_c; };
+
 void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
-               int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
+               int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcBatch& bt = TcBatch{1, 0, 0, 0}) {
+  const bool batched = bt.batch > 1;
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
   int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
   // Short reductions over tall outputs are bound by the epilogue, not the main loop: 128-wide tiles with a
   // two-stage pipeline fit two CTAs per SM (2 x 97 KB shared memory, 2 x 256 TMEM columns), which doubles
   // the epilogue warps per SM.
-  const bool skinny = !x3 && N > 64 && K <= 512 && M >= 128LL * 2 * ctx->sm_count && getenv("TALOS_TC_SKINNY") != nullptr;
+  const bool skinny = !batched && !x3 && N > 64 && K <= 512 && M >= 128LL * 2 * ctx->sm_count && getenv("TALOS_TC_SKINNY") != nullptr;
   if (skinny) bn = 128;   // (takes precedence over the CTA-pair kernel, which needs bn == 256)
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
+  g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
   // 256-wide outputs with at least 256 rows and a long reduction run on CTA pairs (cta_group::2): 256 x 256 tiles
   // halve the operand bytes each SM has to pull per flop.  For short reductions (K = 256: 8 k-blocks a tile) the
   // pair's start-up and cross-CTA hand-offs cost more than that saves (measured 8 % slower at K = 256, 10 % faster
@@ -305,11 +318,11 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // They also need enough 256 x 256 tiles to occupy every CTA pair without splitting K (the split-K weight-gradient
   // shapes have one or two tiles and are faster on 148 independent CTAs than on 74 pairs).
   const bool pair_shape = K >= 1024 && ceil_div(M, 2 * BM) * ceil_div(N, 256) >= ctx->sm_count / 2;
-  const bool pair = bn == 256 && M >= 256 && (pair_shape || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
+  const bool pair = !batched && bn == 256 && M >= 256 && (pair_shape || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
   g.m_tiles = (int)ceil_div(M, pair ? 2 * BM : BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
   int tiles = g.m_tiles * g.n_tiles, splits = 1;
   const int workers = pair ? ctx->sm_count / 2 : ctx->sm_count;   // CTAs, or CTA pairs
-  if (tiles * 2 <= workers && g.kb_total >= 16) {
+  if (!batched && tiles * 2 <= workers && g.kb_total >= 16) {
     splits = (int)std::min<int64_t>(workers / tiles, g.kb_total / 8);
     if (splits < 2) splits = 1;
   }
@@ -318,16 +331,16 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // length of the accumulation chain (measured ~7e-9 relative per k element).  The fp32-faithful
   // mode therefore never chains more than 512 k elements in TMEM; longer reductions are split and
   // the partial sums are added in fp32 (round-to-nearest) by the reduction kernel.
-  if (x3 && g.kb_per_split > 512 / BK) g.kb_per_split = 512 / BK;
+  if (x3 && !batched && g.kb_per_split > 512 / BK) g.kb_per_split = 512 / BK;   // (batched products with K > 512 are not routed here)
   splits = (int)ceil_div(g.kb_total, g.kb_per_split);
   g.splits = splits;
   // kernel-level scratch: [split-K partials][TF32-rounded copy of the small operand]
   const int64_t a_rows = a_mn ? K : M, a_cols = a_mn ? M : K, b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
   const int64_t a_elems = a_rows * a_cols, b_elems = b_rows * b_cols;
-  const bool round_a = !x3 && a_elems <= b_elems && a_elems <= (1 << 20), round_b = !x3 && !round_a && b_elems <= (1 << 20);
+  const bool round_a = !batched && !x3 && a_elems <= b_elems && a_elems <= (1 << 20), round_b = !batched && !x3 && !round_a && b_elems <= (1 << 20);
   const int64_t r_rows = round_a ? a_rows : b_rows, r_cols = round_a ? a_cols : b_cols, r_ld = (r_cols + 3) & ~int64_t(3);
   const size_t partial_bytes = splits > 1 ? ((sizeof(float) * (size_t)splits * M * N + 255) & ~size_t(255)) : 0;
-  const bool presplit = x3 && b_elems <= (1 << 20);
+  const bool presplit = !batched && x3 && b_elems <= (1 << 20);
   const int64_t s_ld = (b_cols + 3) & ~int64_t(3);
   const size_t round_bytes = (round_a || round_b) ? sizeof(float) * (size_t)(r_rows * r_ld) : presplit ? 2 * sizeof(float) * (size_t)(b_rows * s_ld) : 0;
   char* scratch = (partial_bytes + round_bytes) ? (char*)talos_workspace(ctx, partial_bytes + round_bytes) : nullptr;
@@ -347,9 +360,9 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   }
 
   CUtensorMap ta, tb;
-  bool ok = a_mn ? make_tmap(&ta, A, K, M, lda, BK, true) : make_tmap(&ta, A, M, K, lda, BM, false);
+  bool ok = a_mn ? make_tmap(&ta, A, K, M, lda, BK, true, bt.batch, bt.stride_a) : make_tmap(&ta, A, M, K, lda, BM, false, bt.batch, bt.stride_a);
   const int b_box_rows = pair ? bn / 2 : bn;                      // each CTA of a pair stages half of the B columns
-  ok = ok && (b_mn ? make_tmap(&tb, B, K, N, ldb, BK, true) : make_tmap(&tb, B, N, K, ldb, b_box_rows, false));
+  ok = ok && (b_mn ? make_tmap(&tb, B, K, N, ldb, BK, true, bt.batch, bt.stride_b) : make_tmap(&tb, B, N, K, ldb, b_box_rows, false, bt.batch, bt.stride_b));
   CUtensorMap tbl = tb;
   if (presplit) ok = ok && (b_mn ? make_tmap(&tbl, B_lo, K, N, ldb, BK, true) : make_tmap(&tbl, B_lo, N, K, ldb, b_box_rows, false));
   // Results leave through TMA stores when the destination is 16-byte aligned with a 16-byte pitch, N is a
@@ -359,15 +372,17 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   g.tma_out = 0;
   const bool both = epi.act != 0 && epi.aux_in != nullptr && epi.dact != 0;
   const bool epi_aligned = !(((uintptr_t)epi.bias) & 15) && !(((uintptr_t)epi.aux_in) & 15) && !(epi.ld_aux_in & 3);
-  if (splits > 1) { if (!(N & 3)) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, g.partial, splits, M, N, N); } }
-  else if (!(((uintptr_t)C) & 15) && !(ldc & 3) && !(N & 3) && !epi.aux_out && !both && epi_aligned) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, C, 1, M, N, ldc); }
+  if (splits > 1) { if (!(N & 3)) { g.tma_out = 1; ok = ok && make_out_tmap(&tc, g.partial, splits, M, N, N, M * N); } }
+  else if (!(((uintptr_t)C) & 15) && !(ldc & 3) && !(N & 3) && !(batched && (bt.stride_c & 3)) && !epi.aux_out && !both && epi_aligned) {
+    g.tma_out = 1; ok = ok && make_out_tmap(&tc, C, g.batch, M, N, ldc, batched ? bt.stride_c : M * ldc);
+  }
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   if (pair) {
     talos_gemm_tc2_launch(ctx, a_mn, b_mn, x3, presplit, ta, tb, tc, tbl, g, 2 * std::min(tiles * splits, workers));
     if (splits > 1) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
     return;
   }
-  int grid = std::min(tiles * splits, ctx->sm_count * (skinny ? 2 : 1));
+  int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count * (skinny ? 2 : 1));
   if (skinny) { launch_major<128, 2, false, 2>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid); return; }
 #define TALOS_TC_CASE(BNv, ST, ST3)                                                                          \
   if (bn == BNv) {                                                                                           \
@@ -383,8 +398,11 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
 // Start-up self-check: every operand layout in both modes against the fp32 CUDA-core kernel on a
 // shape with ragged edges.  Any mismatch or device-side timeout disables the tensor-core path for
 // this context (the fp32 kernel then serves all modes) instead of returning wrong numbers.
-bool self_check_shape(talos_ctx* ctx, const int M) {
-  const int N = 328, K = 296, LD = 520;
+// With batch > 1 the LD x LD buffers are cut into `batch` members of LD / batch rows each (M, N, K must fit).
+bool self_check_shape(talos_ctx* ctx, const int M, const int N = 328, const int K = 296, const int batch = 1) {
+  const int LD = 520, member_rows = LD / batch;
+  const int64_t stride = (int64_t)member_rows * LD;
+  const TcBatch bt{batch, stride, stride, stride};
   size_t elems = (size_t)LD * LD;
   float *A = nullptr, *B = nullptr, *C0 = nullptr, *C1 = nullptr;
   std::vector<float> h(elems), r0(elems), r1(elems);
@@ -401,23 +419,28 @@ bool self_check_shape(talos_ctx* ctx, const int M) {
     for (int opA = 0; opA < 2 && (pass || dbg); ++opA)
       for (int opB = 0; opB < 2 && (pass || dbg); ++opB) {
         TALOS_CHECK_CUDA(cudaMemsetAsync(C0, 0, elems * 4, ctx->stream));
-        talos_gemm_fp32_launch(ctx, opA, opB, M, N, K, A, LD, 0, B, LD, 0, C0, LD, 0, 1, e);
+        talos_gemm_fp32_launch(ctx, opA, opB, M, N, K, A, LD, stride, B, LD, stride, C0, LD, stride, batch, e);
         TALOS_CHECK_CUDA(cudaMemcpyAsync(r0.data(), C0, elems * 4, cudaMemcpyDeviceToHost, ctx->stream));
         for (int mode = TALOS_MODE_TF32X3; mode <= TALOS_MODE_TF32 && (pass || dbg); ++mode) {
           TALOS_CHECK_CUDA(cudaMemsetAsync(C1, 0, elems * 4, ctx->stream));
-          tc_launch(ctx, opA, opB, M, N, K, A, LD, B, LD, C1, LD, mode, e);
+          tc_launch(ctx, opA, opB, M, N, K, A, LD, B, LD, C1, LD, mode, e, bt);
           TALOS_CHECK_CUDA(cudaMemcpyAsync(r1.data(), C1, elems * 4, cudaMemcpyDeviceToHost, ctx->stream));
           TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
           int32_t st = 0; TALOS_CHECK_CUDA(cudaMemcpy(&st, ctx->dev_status, 4, cudaMemcpyDeviceToHost));
           if (dbg) fprintf(stderr, "[talos self-check] opA=%d opB=%d mode=%d status=%d\n", opA, opB, mode, st);
           if (st != 0) { cudaMemset(ctx->dev_status, 0, 64); pass = false; if (!dbg) break; }
           double num = 0, den = 0;
-          for (int m = 0; m < M; ++m) for (int n = 0; n < N; ++n) { double d = (double)r1[(size_t)m * LD + n] - r0[(size_t)m * LD + n]; num += d * d; den += (double)r0[(size_t)m * LD + n] * r0[(size_t)m * LD + n]; }
+          for (int bz = 0; bz < batch; ++bz)
+            for (int m = 0; m < M; ++m) for (int n = 0; n < N; ++n) {
+              const size_t i = ((size_t)bz * member_rows + m) * LD + n;
+              double d = (double)r1[i] - r0[i]; num += d * d; den += (double)r0[i] * r0[i];
+            }
           double rel = sqrt(num / (den > 0 ? den : 1));
           if (dbg) fprintf(stderr, "[talos self-check]   rel err %.3e  c[0]=%g ref %g c[last]=%g ref %g\n", rel, r1[0], r0[0], r1[(size_t)(M - 1) * LD + N - 1], r0[(size_t)(M - 1) * LD + N - 1]);
           bool good = rel <= (mode == TALOS_MODE_TF32 ? 2e-3 : 5e-6);
           if (!good) { pass = false; if (dbg) { good = true; continue; } }
-          for (int m = 0; m < LD && pass; ++m) for (int n = (m < M ? N : 0); n < LD; ++n) if (r1[(size_t)m * LD + n] != 0.f) { pass = false; break; }   // nothing outside [M,N]
+          for (int m = 0; m < LD && pass; ++m)                                               // nothing outside any member's [M,N]
+            for (int n = ((m % member_rows) < M && m / member_rows < batch ? N : 0); n < LD; ++n) if (r1[(size_t)m * LD + n] != 0.f) { pass = false; break; }
         }
       }
   } catch (const talos_error&) { pass = false; cudaGetLastError(); }
@@ -426,9 +449,10 @@ bool self_check_shape(talos_ctx* ctx, const int M) {
   return pass;
 }
 
-// Rows 200: one-CTA kernels; rows 456: the CTA-pair kernel (two 256-row tiles, the second one ragged).
+// Rows 200: one-CTA kernels; rows 456: the CTA-pair kernel (two 256-row tiles, the second one ragged); then a batch
+// of three small ragged products (tiles must neither read nor write across batch members).
 bool self_check(talos_ctx* ctx) {
-  bool ok = self_check_shape(ctx, 200);
+  bool ok = self_check_shape(ctx, 200) && self_check_shape(ctx, 72, 88, 104, 3);
   g_check_pair = true;
   ok = ok && self_check_shape(ctx, 456);
   g_check_pair = false;
@@ -437,21 +461,42 @@ bool self_check(talos_ctx* ctx) {
 
 }  // namespace
 
-bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
-                          const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
+static bool tc_ready(talos_ctx* ctx) {
   if (ctx->tc_state < 0) return false;
-  // TMA needs 16-byte aligned bases and row pitches; tiny problems are launch-bound and stay on CUDA cores.
-  if ((((uintptr_t)A | (uintptr_t)B) & 15) || (lda & 3) || (ldb & 3) || K < 1) return false;
-  if (M * N * K < (1LL << 18) || M < 1 || N < 1) return false;
   if (getenv("TALOS_DISABLE_TENSOR_CORES")) return false;
   if (ctx->tc_state == 0) {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     cudaStreamIsCapturing(ctx->stream, &cap);
     if (cap != cudaStreamCaptureStatusNone) return false;      // cannot self-check inside a capture
     ctx->tc_state = self_check(ctx) ? 1 : -1;
-    if (ctx->tc_state < 0) return false;
   }
+  return ctx->tc_state > 0;
+}
+
+bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                          const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
+  if (ctx->tc_state < 0) return false;
+  // TMA needs 16-byte aligned bases and row pitches; tiny problems are launch-bound and stay on CUDA cores.
+  if ((((uintptr_t)A | (uintptr_t)B) & 15) || (lda & 3) || (ldb & 3) || K < 1) return false;
+  if (M * N * K < (1LL << 18) || M < 1 || N < 1) return false;
+  if (!tc_ready(ctx)) return false;
   tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, epi);
+  return true;
+}
+
+// Batched product on the one-CTA kernel: the batch index is the third coordinate of every tensor map, so a tile
+// never reads or writes across batch members.  Needs 16-byte aligned strides on top of the plain GEMM's
+// conditions; a 3xTF32 product with K > 512 would need split-K and is left to the fp32 kernel.
+bool talos_gemm_tc_launch_batched(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                                  int64_t strideA, const float* B, int64_t ldb, int64_t strideB, float* C, int64_t ldc, int64_t strideC,
+                                  int64_t batch, int mode, const EpiArgs& epi) {
+  if (ctx->tc_state < 0) return false;
+  if ((((uintptr_t)A | (uintptr_t)B) & 15) || (lda & 3) || (ldb & 3) || (strideA & 3) || (strideB & 3) || K < 1) return false;
+  if (M < 1 || N < 1 || batch < 1 || M * N * K * batch < (1LL << 18) || M * N * K < (1LL << 12)) return false;
+  if (mode == TALOS_MODE_TF32X3 && K > 512) return false;
+  if (ceil_div(M, BM) * ceil_div(N, 32) * batch >= (1LL << 30)) return false;
+  if (!tc_ready(ctx)) return false;
+  tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, epi, TcBatch{batch, strideA, strideB, strideC});
   return true;
 }
 

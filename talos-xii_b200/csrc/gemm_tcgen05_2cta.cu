@@ -29,10 +29,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load whose completion may be signalled on the peer CTA's mbarrier (address in the cluster window).
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+__device__ __forceinline__ void tma_load_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(0) : "memory");   // batch member 0: the pair kernel is not batched
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t* dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
@@ -114,13 +114,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
           if (BPS) {
             uint8_t* bl_dst = sBlo + stage * B_BYTES;
-            if (B_MN) { for (int j = 0; j < BH / 32; ++j) tma_load_2d_pair(bl_dst + j * (BK * 128), &tmap_b_lo, col0 + 32 * j, kb * BK, bar); }
-            else tma_load_2d_pair(bl_dst, &tmap_b_lo, kb * BK, col0, bar);
+            if (B_MN) { for (int j = 0; j < BH / 32; ++j) tma_load_pair(bl_dst + j * (BK * 128), &tmap_b_lo, col0 + 32 * j, kb * BK, bar); }
+            else tma_load_pair(bl_dst, &tmap_b_lo, kb * BK, col0, bar);
           }
-          if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmap_a, row0 + 32 * j, kb * BK, bar); }
-          else tma_load_2d_pair(a_dst, &tmap_a, kb * BK, row0, bar);
-          if (B_MN) { for (int j = 0; j < BH / 32; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &tmap_b, col0 + 32 * j, kb * BK, bar); }
-          else tma_load_2d_pair(b_dst, &tmap_b, kb * BK, col0, bar);
+          if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_pair(a_dst + j * (BK * 128), &tmap_a, row0 + 32 * j, kb * BK, bar); }
+          else tma_load_pair(a_dst, &tmap_a, kb * BK, row0, bar);
+          if (B_MN) { for (int j = 0; j < BH / 32; ++j) tma_load_pair(b_dst + j * (BK * 128), &tmap_b, col0 + 32 * j, kb * BK, bar); }
+          else tma_load_pair(b_dst, &tmap_b, kb * BK, col0, bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -175,7 +175,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
       tc_fence_after();
       tc_epilogue_tile<BN>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32),
-                           (long long)mb * 2 * BM + (long long)rank * BM, nb, ks, store_count);
+                           (long long)mb * 2 * BM + (long long)rank * BM, nb, ks, 0, store_count);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);

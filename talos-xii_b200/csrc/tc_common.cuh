@@ -14,6 +14,8 @@ struct TcArgs {
   EpiArgs epi;
   int32_t* status;
   int tma_out;                             // 1: results leave through TMA stores (tmap_c), 0: direct stores
+  int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
+  long long stride_c;                      // elements between consecutive batch members of C
 };
 
 namespace {
@@ -59,10 +61,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+// Operand tiles: every operand map is [batch][rows][cols]; c2 selects the batch member (0 for a plain GEMM).
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
@@ -183,7 +186,8 @@ __device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restri
 // accumulator's first column, `m_base` the global row of TMEM lane 0, `stage` this warp's 4 KB staging buffer.
 template <int BN>
 __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensorMap* tmap_c, uint32_t t_base, int warp, int lane, float* stage,
-                                                 long long m_base, int nb, int ks, uint32_t& store_count) {
+                                                 long long m_base, int nb, int ks, int bz, uint32_t& store_count) {
+  float* const c_base = g.C + (long long)bz * g.stride_c;   // this batch member's C (split-K never batches: ks or bz is 0)
   // Each warp drains its 32-lane quadrant (one accumulator row per lane) 32 columns at a time.
   const int quad = warp & 3, half = (warp - 2) >> 2;
   const long long m0 = m_base + quad * 32;
@@ -208,7 +212,7 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensor
         const int dact = g.epi.aux_in ? g.epi.dact : 0;
         const float* bias_p = (fuse && g.epi.bias) ? g.epi.bias + n0 : nullptr;
         const float* aux_p = (fuse && dact) ? g.epi.aux_in + m * g.epi.ld_aux_in + n0 : nullptr;
-        const float* cold_p = (fuse && g.epi.beta) ? g.C + m * g.ldc + n0 : nullptr;
+        const float* cold_p = (fuse && g.epi.beta) ? c_base + m * g.ldc + n0 : nullptr;
         const int groups = (int)min((long long)8, (g.N - n0) >> 2);     // N is a multiple of 4 on this path
 #define TALOS_EPI_STORE(A, D)                                                                                           \
   _Pragma("unroll") for (int c = 0; c < 8; ++c) {                                                                      \
@@ -232,7 +236,7 @@ if (fuse && c < groups)                                                         
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) { tma_store_3d(tmap_c, buf, (int)n0, (int)m0, ks); tma_store_commit(); }
+      if (lane == 0) { tma_store_3d(tmap_c, buf, (int)n0, (int)m0, ks + bz); tma_store_commit(); }
       ++store_count;
     } else {
       // Unaligned output: transpose through a padded tile so lanes run along the contiguous axis.
@@ -246,7 +250,7 @@ if (fuse && c < groups)                                                         
 #pragma unroll 4
         for (int rr = 0; rr < rows_valid; ++rr) if (col_ok) P[(long long)rr * g.N] = stage[rr * 32 + (lane ^ rr)];
       } else {
-        epilogue_rows(g.epi, stage, lane, m0, rows_valid, n, col_ok, g.C, g.ldc);
+        epilogue_rows(g.epi, stage, lane, m0, rows_valid, n, col_ok, c_base, g.ldc);
       }
       __syncwarp();
     }

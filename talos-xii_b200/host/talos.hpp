@@ -349,7 +349,7 @@ struct MultiHeadLatentAttention {                                               
       Buf go = make_buf(BH * S * dh, false), gq = make_buf(BH * S * tot, false), gk = make_buf(BH * S * tot, false), gv = make_buf(BH * S * dh, false);
       int64_t bshd[4] = {(int64_t)B, (int64_t)S, (int64_t)H, (int64_t)dh};
       check(talos_transpose(ctx(), o.g(), go->dev, bshd, 4, 1, 2, 0));                // [B,S,H,dh] -> [B,H,S,dh]
-      check(talos_attention_bwd(ctx(), q->dev, k->dev, vv->dev, probs->dev, go->dev, gq->dev, gk->dev, gv->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale));
+      check(talos_attention_bwd(ctx(), q->dev, k->dev, vv->dev, probs->dev, go->dev, gq->dev, gk->dev, gv->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale, mode()));
       auto unpack = [&](const float* src, size_t w, float* ga, float* gb, size_t wa, size_t wb) {   // [B,H,S,w] -> [B,S,H,w] -> split, accumulate
         Buf t = make_buf(B * S * H * w, false);
         int64_t bhsw[4] = {(int64_t)B, (int64_t)H, (int64_t)S, (int64_t)w};
@@ -360,7 +360,7 @@ struct MultiHeadLatentAttention {                                               
       unpack(gq->dev, tot, p[0].g(), p[1].g(), dh, dr); unpack(gk->dev, tot, p[2].g(), p[3].g(), dh, dr); unpack(gv->dev, dh, p[4].g(), nullptr, dh, 0);
     });
     Buf att = make_buf(BH * S * dh, false);
-    check(talos_attention_fwd(ctx(), q->dev, k->dev, vv->dev, att->dev, probs->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale, causal ? 1 : 0));
+    check(talos_attention_fwd(ctx(), q->dev, k->dev, vv->dev, att->dev, probs->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale, causal ? 1 : 0, mode()));
     int64_t bhsd[4] = {(int64_t)B, (int64_t)H, (int64_t)S, (int64_t)dh};
     check(talos_transpose(ctx(), att->dev, out.d(), bhsd, 4, 1, 2, 0));
     Runtime::get().synchronize();

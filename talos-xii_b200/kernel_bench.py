@@ -83,8 +83,10 @@ def main():
     emit(kernel="rope", shape=[Bq, S, H, dr], ms=ms, gbps=gb / (ms * 1e-3), frac_of_hbm=gb / (ms * 1e-3) / hbm, hbm_peak_gbps=hbm, peak_source=src)
     BH, S, dqk, dv = 4096, 128, 96, 64                           # config 4 attention core
     q = torch.randn(BH, S, dqk, device="cuda"); k = torch.randn_like(q); v = torch.randn(BH, S, dv, device="cuda"); o = torch.empty_like(v)
-    ms = timeit(lambda: L.talos_attention_fwd(ctx.handle, P(q), P(k), P(v), P(o), None, BH, S, dqk, dv, 0.1, 0), do_flush=False, reps=5)
-    emit(kernel="attention_fwd", shape=[BH, S, dqk, dv], ms=ms, tflops=2.0 * BH * S * S * (dqk + dv) / (ms * 1e-3) / 1e12)
+    for mname in ("tf32", "tf32x3", "fp32"):
+        md = talos.MODES[mname]
+        ms = timeit(lambda: L.talos_attention_fwd(ctx.handle, P(q), P(k), P(v), P(o), None, BH, S, dqk, dv, 0.1, 0, md), do_flush=False, reps=5)
+        emit(kernel="attention_fwd", mode=mname, shape=[BH, S, dqk, dv], ms=ms, tflops=2.0 * BH * S * S * (dqk + dv) / (ms * 1e-3) / 1e12)
 
 
 if __name__ == "__main__":

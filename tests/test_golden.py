@@ -75,8 +75,8 @@ def test_cuda_path_matches_golden_vectors(talos):
     ctx.synchronize(); assert rel_err(sy, G["sm_y"]) <= 2e-6 and rel_err(sdx, G["sm_dx"]) <= 1e-5
     q, k, v, go = dev(G["att_q"]), dev(G["att_k"]), dev(G["att_v"]), dev(G["att_go"]); O = torch.empty_like(v); Pr = torch.empty(3, 10, 10, device="cuda:0")
     dq = torch.empty_like(q); dk = torch.empty_like(k); dv = torch.empty_like(v); sc = 1.0 / math.sqrt(12.0)
-    L.talos_attention_fwd(ctx.handle, P(q), P(k), P(v), P(O), P(Pr), 3, 10, 12, 6, sc, 0)
-    L.talos_attention_bwd(ctx.handle, P(q), P(k), P(v), P(Pr), P(go), P(dq), P(dk), P(dv), 3, 10, 12, 6, sc)
+    L.talos_attention_fwd(ctx.handle, P(q), P(k), P(v), P(O), P(Pr), 3, 10, 12, 6, sc, 0, 0)
+    L.talos_attention_bwd(ctx.handle, P(q), P(k), P(v), P(Pr), P(go), P(dq), P(dk), P(dv), 3, 10, 12, 6, sc, 0)
     ctx.synchronize()
     for a, name in ((O, "att_O"), (Pr, "att_P"), (dq, "att_dq"), (dk, "att_dk"), (dv, "att_dv")):
         assert rel_err(a, G[name]) <= 2e-5, name

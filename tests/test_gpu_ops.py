@@ -293,26 +293,52 @@ def test_softmax_fwd_bwd(talos, ctx):
     talos.lib.talos_softmax_fwd(ctx.handle, None, None, 5, 0, 1.0, 0)        # empty rows: nothing to do
 
 
-def test_attention_fwd_bwd(talos, ctx):
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_attention_fwd_bwd(talos, ctx, mode):
     import torch
-    for BH, S, dqk, dv, causal in [(5, 3, 12, 8, 0), (16, 64, 32, 32, 1), (6, 128, 96, 64, 0), (3, 100, 40, 24, 0), (4, 17, 8, 130 - 2, 1)]:
+    tol = TOL[mode]
+    # (6,128,96,64) is the MLA shape of config 4, (16,64,32,32) the block of config 3; the ragged ones fall back to
+    # the fused CUDA-core kernel (forward) / the fp32 batched GEMM (backward) in every mode.
+    for BH, S, dqk, dv, causal in [(5, 3, 12, 8, 0), (16, 64, 32, 32, 1), (6, 128, 96, 64, 0), (3, 100, 40, 24, 0), (4, 17, 8, 130 - 2, 1), (300, 16, 32, 16, 0)]:
         q = normal(1, (BH, S, dqk)); k = normal(2, (BH, S, dqk)); v = normal(3, (BH, S, dv)); scale = 1.0 / math.sqrt(dqk)
         sc = orc.bmm_qkt(q, k) * np.float64(np.float32(scale))
         P = orc.softmax(sc, S if causal else 0); O = orc.bmm_pv(P, v)
         out = torch.empty(BH, S, dv, device="cuda:0"); probs = torch.empty(BH, S, S, device="cuda:0")
         dq_, dk_, dv_ = dev(q), dev(k), dev(v)
-        talos.lib.talos_attention_fwd(ctx.handle, talos.ptr(dq_), talos.ptr(dk_), talos.ptr(dv_), talos.ptr(out), talos.ptr(probs), BH, S, dqk, dv, scale, causal)
+        talos.lib.talos_attention_fwd(ctx.handle, talos.ptr(dq_), talos.ptr(dk_), talos.ptr(dv_), talos.ptr(out), talos.ptr(probs), BH, S, dqk, dv, scale, causal, mode)
         ctx.synchronize()
-        assert rel_err(probs, P) <= 1e-5 and rel_err(out, O) <= 1e-5, (BH, S)
+        assert rel_err(probs, P) <= tol and rel_err(out, O) <= tol, (BH, S, rel_err(probs, P), rel_err(out, O))
+        out2 = torch.empty_like(out)                      # without the probabilities: scores go through scratch
+        talos.lib.talos_attention_fwd(ctx.handle, talos.ptr(dq_), talos.ptr(dk_), talos.ptr(dv_), talos.ptr(out2), None, BH, S, dqk, dv, scale, causal, mode)
+        ctx.synchronize()
+        assert torch.equal(out, out2), (BH, S)
         G = normal(4, (BH, S, dv))
         gq = torch.empty_like(dq_); gk = torch.empty_like(dk_); gv = torch.empty_like(dv_)
         talos.lib.talos_attention_bwd(ctx.handle, talos.ptr(dq_), talos.ptr(dk_), talos.ptr(dv_), talos.ptr(probs), dptr(talos, G),
-                                      talos.ptr(gq), talos.ptr(gk), talos.ptr(gv), BH, S, dqk, dv, scale)
+                                      talos.ptr(gq), talos.ptr(gk), talos.ptr(gv), BH, S, dqk, dv, scale, mode)
         ctx.synchronize()
         dP, rdv = orc.bmm_pv_bwd(P, v, G)
         dS = orc.softmax_bwd(P, dP) * np.float64(np.float32(scale))
         rdq, rdk = orc.bmm_qkt_bwd(q, k, dS)
-        assert rel_err(gq, rdq) <= 2e-5 and rel_err(gk, rdk) <= 2e-5 and rel_err(gv, rdv) <= 1e-5, (BH, S)
+        assert rel_err(gq, rdq) <= 2 * tol and rel_err(gk, rdk) <= 2 * tol and rel_err(gv, rdv) <= 2 * tol, (BH, S, rel_err(gq, rdq), rel_err(gk, rdk), rel_err(gv, rdv))
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gemm_batched_all_ops(talos, ctx, mode):
+    import torch
+    # R12 shapes (src/transformer.rs:877-1050) plus ragged ones; beta=1 accumulates into C
+    for batch, M, N, K in [(7, 64, 64, 32), (5, 128, 64, 128), (3, 72, 88, 104), (9, 33, 20, 12), (130, 16, 16, 16)]:
+        for opA, opB in [(0, 0), (0, 1), (1, 0), (1, 1)]:
+            A = normal(10 + M, (batch, K, M) if opA else (batch, M, K)); B = normal(20 + N, (batch, N, K) if opB else (batch, K, N))
+            C0 = normal(30, (batch, M, N))
+            a, b = dev(A), dev(B)
+            for beta in (0, 1):
+                c = dev(C0)
+                talos.lib.talos_gemm_batched(ctx.handle, opA, opB, M, N, K, talos.ptr(a), A.shape[2], A.shape[1] * A.shape[2],
+                                             talos.ptr(b), B.shape[2], B.shape[1] * B.shape[2], talos.ptr(c), N, M * N, batch, beta, mode)
+                ctx.synchronize()
+                ref = np.einsum("bmk,bkn->bmn", np.swapaxes(A, 1, 2) if opA else A, np.swapaxes(B, 1, 2) if opB else B) + (C0 if beta else 0)
+                assert rel_err(c, ref) <= TOL[mode], (batch, M, N, K, opA, opB, beta, rel_err(c, ref))
 
 
 def test_layout_ops(talos, ctx):
