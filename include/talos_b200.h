@@ -188,6 +188,26 @@ talos_status talos_attention_bwd(talos_ctx* ctx, const float* q, const float* k,
                                  const float* probs, const float* dout, float* dq, float* dk, float* dv,
                                  int64_t BH, int64_t S, int64_t dqk, int64_t dvdim, float scale, int32_t mode);
 
+/* ---- batched rollout inference ------------------------------------------------------------ */
+/* One decode step of MultiHeadLatentAttention::forward_inference_cached (src/transformer.rs:688-841)
+ * for N independent simulations at once -- the attention part of ActorCritic::step_inference_cached
+ * (src/ppo.rs:391-432) as the simulator calls it once per pull (src/sim.rs:208), followed by the
+ * sliding-window prune (src/transformer.rs:843-874, src/sim.rs:171-175, :578).
+ *   q_c, k_c, v_c [N, H*dh], q_r, k_r [N, H*dr]: the five projections of the new token (Linear outputs);
+ *   pos [N] (device): each simulation's absolute token position (the `start_pos` argument);
+ *   k_cache [N,H,cap,dh+dr], v_cache [N,H,cap,dh]: per-simulation rings, cap = context_len + 1;
+ *   out [N, H*dh]: attention output, ready for w_o.
+ * Rotates q_r and k_r by pos (interleaved pairs, positions past the table unrotated), writes
+ * k = [k_c | rot(k_r)] and v_c into ring slot pos % cap, attends over the min(pos+1, cap) live slots
+ * with `scale`.  Does not change pos: call talos_decode_advance after the step. */
+talos_status talos_mla_decode_step(talos_ctx* ctx, const float* q_c, const float* q_r, const float* k_c, const float* k_r,
+                                   const float* v_c, const float* cos_t, const float* sin_t, int64_t table_len,
+                                   const int32_t* pos, float* k_cache, float* v_cache, float* out, int64_t N, int64_t H,
+                                   int64_t dh, int64_t dr, int64_t cap, float scale);
+/* pos[n] = reset[n] ? 0 : pos[n] + 1.  reset (nullable, device): simulations that start a new episode,
+ * i.e. whose KVCache the simulator clears (src/transformer.rs:420-424). */
+talos_status talos_decode_advance(talos_ctx* ctx, int32_t* pos, const int32_t* reset, int64_t N);
+
 /* ---- layout ops --------------------------------------------------------------------------- */
 /* Tensor::transpose (src/autograd.rs:632-739): swap two axes of a rank<=6 tensor (full copy).
  * accumulate=1 adds into y (its backward). `shape` is the INPUT shape, host memory. */

@@ -293,6 +293,37 @@ class ActorCritic:
         last = seq[:, -1, :]                                   # last_token :92-109
         return linear_fwd(last, *self.actor).reshape(-1)
 
+    def step_probs_inference_cached(self, state, cache, start_pos):
+        """The deterministic part of step_inference_cached (src/ppo.rs:391-412): one token through the KV-cached
+        backbone, actor head, softmax with max subtraction.  (The sampling that follows uses rand::random and is
+        outside parity.)"""
+        last = self.backbone.forward_inference_step(state, cache, start_pos)
+        logits = linear_forward_inference(last, *self.actor)
+        e = np.exp(logits - logits.max())
+        return e / e.sum()
+
+
+def rollout_reference(ac, states, resets, context_len):
+    """What the simulator does with the cached policy for each of N simulations independently
+    (src/sim.rs:208, :578, :171-175): step t calls step_inference_cached(state, cache, start_pos = pulls done
+    in this episode), then prunes the cache to `context_len`; resets[t, n] != 0 ends simulation n's episode
+    after step t (fresh KVCache, start_pos back to 0).  states [T, N, in]; returns probabilities [T, N, A]."""
+    T, N, _ = states.shape
+    caches = [KVCache(ac.backbone.cfg.num_heads) for _ in range(N)]
+    pos = [0] * N
+    out = []
+    for t in range(T):
+        row = []
+        for n in range(N):
+            row.append(ac.step_probs_inference_cached(states[t, n], caches[n], pos[n]))
+            prune_kv_cache(caches[n], ac.backbone.cfg, context_len)
+            if resets[t, n]:
+                caches[n] = KVCache(ac.backbone.cfg.num_heads); pos[n] = 0
+            else:
+                pos[n] += 1
+        out.append(row)
+    return np.array(out)
+
 # ------------------------------------------------------------------ plain multi-head block (BASELINE config 3) -- extension
 
 

@@ -521,6 +521,72 @@ struct ActorCritic {                                                            
   std::vector<Tensor> parameters() const { auto p = backbone.parameters(); for (auto& t : actor_head.parameters()) p.push_back(t); for (auto& t : critic_head.parameters()) p.push_back(t); return p; }
 };
 
+// ActorCritic::step_inference_cached (src/ppo.rs:391-432) for N simulations at once: what the simulator does once
+// per pull and per simulation (src/sim.rs:208, then prune_cache at :578) becomes one GEMM per layer over all
+// simulations plus one attention kernel over per-simulation KV rings.  Graph-free; every buffer is allocated once.
+// A ring of context_len + 1 slots reproduces "append, attend, prune to context_len".  Sampling stays with the
+// caller (the crate uses rand::random there): step() returns the action probabilities.
+struct BatchedRollout {
+  const ActorCritic& ac; size_t n, context_len, cap;
+  Buf k_cache, v_cache, pos, reset_dev;                       // pos / reset_dev hold int32 values
+  Buf x, h, hn, c_kv, k_c, v_c, k_r, q_c, q_r, att, ao, h2, f1, f2, h3, o, logits, probs;
+  BatchedRollout(const ActorCritic& policy, size_t sims, size_t ctx_len) : ac(policy), n(sims), context_len(ctx_len), cap(ctx_len + 1) {
+    const MLAConfig& c = ac.backbone.mla_layer.config;
+    const size_t H = c.num_heads, dh = c.v_head_dim, dr = c.qk_rope_dim, D = c.dim;
+    k_cache = make_buf(n * H * cap * (dh + dr)); v_cache = make_buf(n * H * cap * dh); pos = make_buf(n); reset_dev = make_buf(n);
+    x = make_buf(n * ActorCritic::DIM, false); h = make_buf(n * D, false); hn = make_buf(n * D, false); c_kv = make_buf(n * c.kv_lora_rank, false);
+    k_c = make_buf(n * H * dh, false); v_c = make_buf(n * H * dh, false); q_c = make_buf(n * H * dh, false);
+    k_r = make_buf(n * H * dr, false); q_r = make_buf(n * H * dr, false); att = make_buf(n * H * dh, false); ao = make_buf(n * D, false);
+    h2 = make_buf(n * D, false); f1 = make_buf(n * 2 * D, false); f2 = make_buf(n * D, false); h3 = make_buf(n * D, false); o = make_buf(n * D, false);
+    logits = make_buf(n * ActorCritic::ACTION_SPACE, false); probs = make_buf(n * ActorCritic::ACTION_SPACE, false);
+  }
+  void reset_all() { check(talos_memset_zero(ctx(), pos->dev, sizeof(float) * n)); }     // every simulation starts a new episode
+  // One policy step for all simulations.  `states_dev`: [N, DIM] fp32 on the device.  `reset_after` (nullable, N
+  // entries): simulations whose episode ends with this step.  Returns the device buffer of probabilities [N, A].
+  const float* step(const float* states_dev, const std::vector<int32_t>* reset_after = nullptr) {
+    const LuckTransformer& t = ac.backbone; const MultiHeadLatentAttention& m = t.mla_layer; const MLAConfig& c = m.config;
+    const size_t H = c.num_heads, dh = c.v_head_dim, dr = c.qk_rope_dim, D = c.dim;
+    auto lin = [&](const Linear& l, const float* in, float* out, int act = TALOS_ACT_NONE) {
+      check(talos_linear_fwd(ctx(), in, l.weight.d(), l.bias ? l.bias->d() : nullptr, out, nullptr, (int64_t)n, (int64_t)l.in_features, (int64_t)l.out_features, act, mode()));
+    };
+    auto norm = [&](const RMSNorm& r, const float* in, float* out) {
+      check(talos_rmsnorm_fwd(ctx(), in, r.weight.d(), (float)r.eps, (int64_t)n, (int64_t)r.dim, out, nullptr));
+    };
+    lin(t.embed, states_dev, h->dev);                                                 // src/transformer.rs:159-160
+    norm(t.norm_1, h->dev, hn->dev);
+    lin(m.w_dkv, hn->dev, c_kv->dev); lin(m.w_uk, c_kv->dev, k_c->dev); lin(m.w_uv, c_kv->dev, v_c->dev);   // :705-710
+    lin(m.w_kr, hn->dev, k_r->dev); lin(m.w_q, hn->dev, q_c->dev); lin(m.w_qr, hn->dev, q_r->dev);
+    check(talos_mla_decode_step(ctx(), q_c->dev, q_r->dev, k_c->dev, k_r->dev, v_c->dev, m.rope.cos_cache->dev, m.rope.sin_cache->dev,
+                                (int64_t)(m.rope.max_len * dr / 2), (const int32_t*)pos->dev, k_cache->dev, v_cache->dev, att->dev, (int64_t)n, (int64_t)H,
+                                (int64_t)dh, (int64_t)dr, (int64_t)cap, 1.f / std::sqrt((float)(dh + dr))));
+    lin(m.w_o, att->dev, ao->dev);
+    check(talos_eltwise_binary(ctx(), TALOS_EW_ADD, h->dev, ao->dev, h2->dev, (int64_t)(n * D)));            // :166-170
+    norm(t.norm_2, h2->dev, hn->dev);
+    lin(t.ffn_1, hn->dev, f1->dev, TALOS_ACT_RELU); lin(t.ffn_2, f1->dev, f2->dev);                          // :174-183
+    check(talos_eltwise_binary(ctx(), TALOS_EW_ADD, h2->dev, f2->dev, h3->dev, (int64_t)(n * D)));
+    norm(t.norm_final, h3->dev, hn->dev);
+    lin(t.out_proj, hn->dev, o->dev);
+    lin(ac.actor_head, o->dev, logits->dev);                                          // src/ppo.rs:400
+    check(talos_softmax_fwd(ctx(), logits->dev, probs->dev, (int64_t)n, (int64_t)ActorCritic::ACTION_SPACE, 1.f, 0));
+    const int32_t* rs = nullptr;
+    if (reset_after) {
+      TALOS_ASSERT(reset_after->size() == n, "reset mask must have one entry per simulation");
+      check(talos_copy_from_host(ctx(), reset_dev->dev, reset_after->data(), sizeof(int32_t) * n));
+      rs = (const int32_t*)reset_dev->dev;
+    }
+    check(talos_decode_advance(ctx(), (int32_t*)pos->dev, rs, (int64_t)n));
+    return probs->dev;
+  }
+  std::vector<double> step_host(const std::vector<double>& states, const std::vector<int32_t>* reset_after = nullptr) {
+    TALOS_ASSERT(states.size() == n * ActorCritic::DIM, "states must be [N, DIM]");
+    check(talos_upload_f64(ctx(), x->dev, states.data(), (int64_t)states.size()));
+    const float* p = step(x->dev, reset_after);
+    std::vector<double> out(n * ActorCritic::ACTION_SPACE);
+    check(talos_download_f64(ctx(), out.data(), p, (int64_t)out.size()));
+    return out;
+  }
+};
+
 struct Adam {                                                                       // src/ppo.rs:482-540; clip_norm = 1 gives src/dqn.rs:207-239
   std::vector<Tensor> params; std::vector<Buf> m, v; size_t t = 0; double lr, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, clip_norm = 0.0;
   Adam(std::vector<Tensor> p, double learning_rate) : params(std::move(p)), lr(learning_rate) { for (auto& q : params) { m.push_back(make_buf(q.len())); v.push_back(make_buf(q.len())); } }

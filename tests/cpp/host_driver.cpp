@@ -7,6 +7,11 @@
 //                                        upstream gradient seed 15); loss = sum(out*G); writes fp32: out, dx (first dumpB
 //                                        samples each), then the six parameter gradients.
 //   mla4  <dumpB> <B> <token>          : benchmark config 4 (S128 d512 r64 H8 dh64 dr32, seeds 20-27) forward; writes fp32 out.
+//   rollout <seed> <N> <T> <ctx> [time]: ActorCritic(seed) stepped T times over N simulations through BatchedRollout
+//                                        (KV rings of ctx+1 slots); states N(0, 0.5^2) seed+500 as [T,N,8]; simulation n
+//                                        ends an episode after step t when (t*7 + n*3) % 11 == 0; writes f64 probabilities
+//                                        [T,N,5].  With `time`: no dump, prints simulation-steps per second instead.
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -71,6 +76,36 @@ int main(int argc, char** argv) {
       Tensor x = normal({Bn, Sq, D}, 20, 1.f);
       Tensor out = m.forward(x);
       dump32(f, out.to_vec(), dumpB * Sq * D);
+    } else if (what == "rollout") {
+      const size_t N = B, T = S, ctx_len = std::stoul(argv[7]);
+      const bool timing = argc > 8 && std::string(argv[8]) == "time";
+      ActorCritic ac(seed);
+      if (sym) {
+        LuckTransformer& t = ac.backbone;
+        for (Linear* l : {&t.embed, &t.ffn_1, &t.ffn_2, &t.out_proj, &t.mla_layer.w_dkv, &t.mla_layer.w_uk, &t.mla_layer.w_uv, &t.mla_layer.w_q,
+                          &t.mla_layer.w_kr, &t.mla_layer.w_qr, &t.mla_layer.w_o, &ac.actor_head}) symmetrise(*l);
+      }
+      BatchedRollout roll(ac, N, ctx_len);
+      if (!timing) {
+        Tensor states = normal({T, N, ActorCritic::DIM}, seed + 500, 0.5f);
+        const std::vector<double> sv = states.to_vec();
+        for (size_t t = 0; t < T; ++t) {
+          std::vector<int32_t> reset(N);
+          for (size_t n = 0; n < N; ++n) reset[n] = ((t * 7 + n * 3) % 11 == 0) ? 1 : 0;
+          std::vector<double> st(sv.begin() + t * N * ActorCritic::DIM, sv.begin() + (t + 1) * N * ActorCritic::DIM);
+          dump(f, roll.step_host(st, &reset));
+        }
+      } else {
+        Tensor states = normal({N, ActorCritic::DIM}, seed + 500, 0.5f);
+        for (size_t t = 0; t < 3; ++t) roll.step(states.d());
+        Runtime::get().synchronize();
+        const auto t0 = std::chrono::steady_clock::now();          // host clock between two stream synchronisations
+        for (size_t t = 0; t < T; ++t) roll.step(states.d());
+        Runtime::get().synchronize();
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        std::printf("{\"kernel\": \"batched_rollout_step\", \"sims\": %zu, \"context_len\": %zu, \"steps\": %zu, \"ms_per_step\": %.4f, \"sim_steps_per_s\": %.1f}\n",
+                    N, ctx_len, T, ms / T, (double)N * T / (ms * 1e-3));
+      }
     } else { return 4; }
     std::fclose(f);
   } catch (const std::exception& e) { std::fprintf(stderr, "host_driver: %s\n", e.what()); return 1; }

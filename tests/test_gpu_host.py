@@ -138,3 +138,29 @@ def test_config4_mla_forward_both_position_modes(mode, tol):
         full = run_driver32(["mla4", mode, Bs, 512, 1]).reshape(outs[1].shape)    # full batch 512: first samples unchanged
         # (tile shapes and split-K differ with the batch size, so agreement is to the mode's tolerance, not bit-exact)
         assert np.linalg.norm(full - outs[1]) <= tol * np.linalg.norm(outs[1])
+
+
+@pytest.mark.parametrize("mode,tol", [(0, 1e-5), (1, 1e-5), (2, 2e-3)])
+def test_batched_rollout_matches_per_simulation_cached_inference(mode, tol):
+    # ActorCritic::step_inference_cached (src/ppo.rs:391-432) + prune_cache (src/sim.rs:171-175) per simulation in the
+    # oracle vs. one batched step over all simulations on the device.  23 steps with a context of 6 make every ring
+    # wrap several times; the reset pattern leaves the simulations at different positions; N = 37 is not a multiple
+    # of the kernel's 8 warps per block.
+    seed, N, T, ctx = 42, 37, 23, 6
+    got = run_driver(["rollout", mode, seed, N, T, ctx]).reshape(T, N, 5)
+    ac = om.ActorCritic(seed)
+    bb = ac.backbone
+    for name in ("embed", "ffn_1", "ffn_2", "out_proj"):
+        W, b = getattr(bb, name); setattr(bb, name, (sym(W, *W.shape), b))
+    bb.mla = {k: sym(v, *v.shape) for k, v in bb.mla.items()}
+    ac.actor = (sym(ac.actor[0], *ac.actor[0].shape), ac.actor[1])
+    states = nrm(seed + 500, (T, N, 8), 0.5)
+    resets = np.array([[1 if (t * 7 + n * 3) % 11 == 0 else 0 for n in range(N)] for t in range(T)])
+    ref = om.rollout_reference(ac, states, resets, ctx)
+    err = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert err <= tol, err
+    assert np.abs(got.sum(-1) - 1.0).max() < 1e-5
+    if mode != 2:   # identical argmax wherever the oracle's top two probabilities are not within rounding of each other
+        top2 = np.sort(ref, -1)[..., -2:]
+        clear = (top2[..., 1] - top2[..., 0]) > 1e-4
+        assert np.array_equal(got.argmax(-1)[clear], ref.argmax(-1)[clear])
