@@ -188,6 +188,20 @@ talos_status talos_attention_bwd(talos_ctx* ctx, const float* q, const float* k,
                                  const float* probs, const float* dout, float* dq, float* dk, float* dv,
                                  int64_t BH, int64_t S, int64_t dqk, int64_t dvdim, float scale, int32_t mode);
 
+/* ---- advantage estimation (src/ppo.rs:650-675) --------------------------------------------- */
+/* Reward normalisation with the running statistics (RunningMeanStd::normalize, src/ppo.rs:476-478:
+ * (r - mean) / (sqrt(var) + 1e-8)), clipped to +-10 (:655), then the reverse GAE scan over the whole
+ * rollout buffer (:658-671): delta = r + gamma * V[t+1] * nonterminal - V[t] with V[len] = 0,
+ * gae = delta + gamma * lambda * nonterminal * gae_next; advantages[t] = gae, returns[t] = gae + V[t].
+ * terminals: int32, non-zero where is_terminals[t].  The crate's constants are gamma 0.99,
+ * lambda 0.95 (:18-19).  All arrays on the device, length len. */
+talos_status talos_gae(talos_ctx* ctx, const float* rewards, const float* values, const int32_t* terminals, int64_t len,
+                       float gamma, float lambda, float rew_mean, float rew_var, float* advantages, float* returns);
+/* Advantage normalisation (src/ppo.rs:673-675, sum_f64 / sum_sq_diff / normalize_slice at :24-244):
+ * y = (x - mean) / (sqrt(sum((x - mean)^2) / n) + 1e-8).  stats (nullable, device, 2 floats) receives
+ * the mean and that denominator.  y may alias x. */
+talos_status talos_normalize_slice(talos_ctx* ctx, const float* x, int64_t n, float* y, float* stats);
+
 /* ---- batched rollout inference ------------------------------------------------------------ */
 /* One decode step of MultiHeadLatentAttention::forward_inference_cached (src/transformer.rs:688-841)
  * for N independent simulations at once -- the attention part of ActorCritic::step_inference_cached

@@ -14,6 +14,7 @@ import ctypes as C
 import os
 import subprocess
 
+import math
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -102,6 +103,30 @@ def normalize_slice(v, mean, std):
     v = _f64(v); out = np.empty_like(v)
     _lib.orc_normalize_slice(_p(v), _p(out), C.c_double(mean), C.c_double(std), C.c_long(v.size))
     return out
+
+
+def gae(rewards, values, terminals, rew_mean, rew_var, gamma=0.99, lam=0.95):
+    """Reward normalisation + reverse GAE scan (src/ppo.rs:650-671; GAMMA, GAE_LAMBDA at :18-19).  Returns
+    (advantages, returns)."""
+    r = _f64(rewards); v = _f64(values); t = np.ascontiguousarray(terminals, dtype=np.int32)
+    adv = np.empty_like(r); ret = np.empty_like(r)
+    _lib.orc_gae(_p(r), _p(v), t.ctypes.data_as(C.POINTER(C.c_int32)), C.c_long(r.size), C.c_double(gamma), C.c_double(lam),
+                 C.c_double(rew_mean), C.c_double(rew_var), _p(adv), _p(ret))
+    return adv, ret
+
+
+class RunningMeanStd:
+    """src/ppo.rs:444-480: count starts at 1e-4, mean 0, var 1; update() folds in one reward at a time."""
+
+    def __init__(self):
+        self.count, self.mean, self.var = C.c_double(1e-4), C.c_double(0.0), C.c_double(1.0)
+
+    def update(self, xs):
+        x = _f64(np.atleast_1d(xs))
+        _lib.orc_running_mean_std_update(C.byref(self.count), C.byref(self.mean), C.byref(self.var), _p(x), C.c_long(x.size))
+
+    def normalize(self, x):
+        return (x - self.mean.value) / (math.sqrt(self.var.value) + 1e-8)
 
 # ---------------------------------------------------------------- autograd.rs
 

@@ -127,6 +127,35 @@ ORC_API void orc_normalize_slice(const double* v, double* out, double mean, doub
   for (long i = 0; i < n; ++i) out[i] = (v[i] - mean) / std;
 }
 
+/* src/ppo.rs:444-480  RunningMeanStd: one-sample Welford-style update and the normalisation that uses it. */
+ORC_API void orc_running_mean_std_update(double* count, double* mean, double* var, const double* x, long n) {
+  for (long i = 0; i < n; ++i) {
+    const double delta = x[i] - *mean, tot = *count + 1.0;
+    const double new_mean = *mean + delta * 1.0 / tot;
+    const double m2 = *var * *count + 0.0 * 1.0 + delta * delta * *count * 1.0 / tot;
+    *mean = new_mean; *var = m2 / tot; *count = tot;
+  }
+}
+
+/* src/ppo.rs:650-671  reward normalisation (clipped to +-10) and the reverse GAE scan over the whole rollout buffer:
+ * delta = r_norm + gamma * V[t+1] * nonterminal - V[t];  gae = delta + gamma * lambda * nonterminal * gae_next;
+ * V[len] = 0; advantages[t] = gae; returns[t] = gae + V[t]. */
+ORC_API void orc_gae(const double* rewards, const double* values, const int32_t* terminals, long len, double gamma, double lambda,
+                     double rew_mean, double rew_var, double* advantages, double* returns) {
+  double last = 0.0;
+  const double denom = sqrt(rew_var) + 1e-8;
+  for (long t = len - 1; t >= 0; --t) {
+    double r = (rewards[t] - rew_mean) / denom;
+    if (r < -10.0) r = -10.0;
+    if (r > 10.0) r = 10.0;
+    const double nt = terminals[t] ? 0.0 : 1.0;
+    const double v = values[t], vn = t < len - 1 ? values[t + 1] : 0.0;
+    const double delta = r + gamma * vn * nt - v;
+    const double gae = delta + gamma * lambda * nt * last;
+    advantages[t] = gae; returns[t] = gae + v; last = gae;
+  }
+}
+
 /* ------------------------------------------------------------------------- */
 /* src/autograd.rs                                                             */
 

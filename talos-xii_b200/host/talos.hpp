@@ -521,6 +521,34 @@ struct ActorCritic {                                                            
   std::vector<Tensor> parameters() const { auto p = backbone.parameters(); for (auto& t : actor_head.parameters()) p.push_back(t); for (auto& t : critic_head.parameters()) p.push_back(t); return p; }
 };
 
+// RunningMeanStd (src/ppo.rs:444-480): host arithmetic in f64 exactly as the crate (a few scalars per reward).
+struct RunningMeanStd {
+  double count = 1e-4, mean = 0.0, var = 1.0;
+  void update(double x) {
+    const double delta = x - mean, tot = count + 1.0;
+    const double m2 = var * count + delta * delta * count / tot;
+    mean += delta / tot; var = m2 / tot; count = tot;
+  }
+  double normalize(double x) const { return (x - mean) / (std::sqrt(var) + 1e-8); }
+};
+
+// The advantage block of PPO::update (src/ppo.rs:650-675) on the device: normalised, clipped rewards -> reverse GAE
+// scan -> returns; advantages normalised with the population standard deviation.  Returns {norm_advantages, returns}.
+inline std::pair<Tensor, Tensor> gae_advantages(const Tensor& rewards, const Tensor& values, const std::vector<int32_t>& is_terminals,
+                                                const RunningMeanStd& reward_normalizer, double gamma = 0.99, double lambda = 0.95) {
+  const size_t len = rewards.len();
+  TALOS_ASSERT(values.len() == len && is_terminals.size() == len, "rollout buffers must have one entry per step");
+  Tensor adv = Tensor::zeros({len}), ret = Tensor::zeros({len});
+  if (len == 0) return {adv, ret};
+  Buf term = make_buf(len, false);
+  check(talos_copy_from_host(ctx(), term->dev, is_terminals.data(), sizeof(int32_t) * len));
+  check(talos_gae(ctx(), rewards.d(), values.d(), (const int32_t*)term->dev, (int64_t)len, (float)gamma, (float)lambda, (float)reward_normalizer.mean,
+                  (float)reward_normalizer.var, adv.d(), ret.d()));
+  check(talos_normalize_slice(ctx(), adv.d(), (int64_t)len, adv.d(), nullptr));
+  Runtime::get().synchronize();                                                   // `term` is released at scope exit
+  return {adv, ret};
+}
+
 // ActorCritic::step_inference_cached (src/ppo.rs:391-432) for N simulations at once: what the simulator does once
 // per pull and per simulation (src/sim.rs:208, then prune_cache at :578) becomes one GEMM per layer over all
 // simulations plus one attention kernel over per-simulation KV rings.  Graph-free; every buffer is allocated once.

@@ -81,6 +81,15 @@ def main():
     ms = timeit(lambda: L.talos_rope(ctx.handle, P(xr), P(yr), P(c), P(sn), c.numel(), Bq, S, H, dr, 0, 0, 0), do_flush=False)
     gb = 2.0 * xr.numel() * 4 / 1e9
     emit(kernel="rope", shape=[Bq, S, H, dr], ms=ms, gbps=gb / (ms * 1e-3), frac_of_hbm=gb / (ms * 1e-3) / hbm, hbm_peak_gbps=hbm, peak_source=src)
+    n = 1 << (22 if args.quick else 25)                          # rollout buffer: GAE scan + advantage normalisation
+    rw = torch.randn(n, device="cuda"); vl = torch.randn(n, device="cuda"); tm = (torch.rand(n, device="cuda") < 0.02).to(torch.int32)
+    adv = torch.empty(n, device="cuda"); ret = torch.empty(n, device="cuda")
+    ms = timeit(lambda: L.talos_gae(ctx.handle, P(rw), P(vl), P(tm), n, 0.99, 0.95, 0.0, 1.0, P(adv), P(ret)), do_flush=False)
+    gb = (2 * 12.0 + 8.0) * n / 1e9                               # two passes read r, V, terminal; the second writes A and R
+    emit(kernel="gae", shape=[n], ms=ms, gbps=gb / (ms * 1e-3), frac_of_hbm=gb / (ms * 1e-3) / hbm, hbm_peak_gbps=hbm, peak_source=src)
+    ms = timeit(lambda: L.talos_normalize_slice(ctx.handle, P(adv), n, P(ret), None), do_flush=False)
+    gb = 16.0 * n / 1e9                                           # three reads, one write
+    emit(kernel="normalize_slice", shape=[n], ms=ms, gbps=gb / (ms * 1e-3), frac_of_hbm=gb / (ms * 1e-3) / hbm, hbm_peak_gbps=hbm, peak_source=src)
     BH, S, dqk, dv = 4096, 128, 96, 64                           # config 4 attention core
     q = torch.randn(BH, S, dqk, device="cuda"); k = torch.randn_like(q); v = torch.randn(BH, S, dv, device="cuda"); o = torch.empty_like(v)
     for mname in ("tf32", "tf32x3", "fp32"):

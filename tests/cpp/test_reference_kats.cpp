@@ -137,6 +137,22 @@ int main(int argc, char** argv) {
     EXPECT(diff < 1e-6);
     policy.backbone.mla_layer.prune_kv_cache(kv, 4); EXPECT(kv.len == 4);           // sliding window, src/transformer.rs:843-874
   });
+  run("ppo: advantage block (reward normalisation, GAE, advantage normalisation)", [] {   // src/ppo.rs:444-480, :650-675
+    RunningMeanStd rn; for (double r : {1.0, 2.0, -1.0}) rn.update(r);
+    EXPECT(std::fabs(rn.count - 3.0001) < 1e-12);
+    const std::vector<double> r{1.0, 2.0, -1.0, 0.5}, v{0.5, 0.25, 0.125, -0.25}; const std::vector<int32_t> term{0, 1, 0, 0};
+    // the same arithmetic in f64, written out
+    std::vector<double> adv(4), ret(4); double last = 0.0;
+    for (int t = 3; t >= 0; --t) {
+      const double nr = std::min(10.0, std::max(-10.0, rn.normalize(r[t]))), nt = term[t] ? 0.0 : 1.0, vn = t < 3 ? v[t + 1] : 0.0;
+      const double gae = nr + 0.99 * vn * nt - v[t] + 0.99 * 0.95 * nt * last;
+      adv[t] = gae; ret[t] = gae + v[t]; last = gae;
+    }
+    double m = 0; for (double a : adv) m += a; m /= 4; double sd = 0; for (double a : adv) sd += (a - m) * (a - m); sd = std::sqrt(sd / 4) + 1e-8;
+    auto got = gae_advantages(Tensor::new_(r, {4}), Tensor::new_(v, {4}), term, rn);
+    const std::vector<double> ga = got.first.to_vec(), gr = got.second.to_vec();
+    for (int t = 0; t < 4; ++t) { EXPECT(std::fabs(ga[t] - (adv[t] - m) / sd) < 1e-5); EXPECT(std::fabs(gr[t] - ret[t]) < 1e-5); }
+  });
   run("dqn: dueling network consumer (batch 64) trains", [] {            // src/dqn.rs:68-107, :207-239, :482-584
     Linear l1(8, 64, true, 1), l2(64, 64, true, 2), val(64, 1, true, 3), adv(64, 5, true, 4);
     auto fwd = [&](const Tensor& s) {

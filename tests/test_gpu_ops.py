@@ -341,6 +341,53 @@ def test_gemm_batched_all_ops(talos, ctx, mode):
                 assert rel_err(c, ref) <= TOL[mode], (batch, M, N, K, opA, opB, beta, rel_err(c, ref))
 
 
+def test_gae_and_advantage_normalisation(talos, ctx):
+    import torch
+    # lengths around the 2 048-element scan chunk and a rollout-sized buffer; episode ends every ~50 steps
+    for n in (1, 7, 2047, 2048, 2049, 50000, 1048576):
+        r = orc.f32r(orc.rng_normal(70, (n,)) * 3.0 + 1.0); v = orc.f32r(orc.rng_normal(71, (n,)))
+        term = (orc.rng_bounded(72, n, 50) == 0).astype(np.int32)
+        rms = orc.RunningMeanStd(); rms.update(r[:min(n, 4096)])
+        mean, var = float(np.float32(rms.mean.value)), float(np.float32(rms.var.value))
+        adv_ref, ret_ref = orc.gae(r, v, term, mean, var)
+        d_r, d_v = dev(r), dev(v); d_t = torch.from_numpy(term).cuda()
+        adv = torch.empty(n, device="cuda:0"); ret = torch.empty(n, device="cuda:0")
+        talos.lib.talos_gae(ctx.handle, talos.ptr(d_r), talos.ptr(d_v), talos.ptr(d_t), n, 0.99, 0.95, mean, var, talos.ptr(adv), talos.ptr(ret))
+        ctx.synchronize()
+        assert rel_err(adv, adv_ref) <= 1e-5 and rel_err(ret, ret_ref) <= 1e-5, (n, rel_err(adv, adv_ref))
+        if n > 1:
+            m = orc.sum_f64(adv_ref) / n; sd = math.sqrt(orc.sum_sq_diff(adv_ref, m) / n) + 1e-8
+            norm_ref = orc.normalize_slice(adv_ref, m, sd)
+            stats = torch.empty(2, device="cuda:0")
+            talos.lib.talos_normalize_slice(ctx.handle, talos.ptr(adv), n, talos.ptr(adv), talos.ptr(stats))      # in place
+            ctx.synchronize()
+            assert rel_err(adv, norm_ref) <= 1e-5, (n, rel_err(adv, norm_ref))
+            st = host(stats); assert abs(st[0] - m) <= 1e-5 * max(1.0, abs(m)) + 1e-6 and abs(st[1] - sd) <= 1e-5 * sd
+    # no episode boundary at all and all boundaries: the two extremes of the recurrence
+    n = 5000; r = orc.f32r(orc.rng_normal(73, (n,))); v = orc.f32r(orc.rng_normal(74, (n,)))
+    for term in (np.zeros(n, np.int32), np.ones(n, np.int32)):
+        adv_ref, ret_ref = orc.gae(r, v, term, 0.0, 1.0)
+        d_r, d_v = dev(r), dev(v); d_t = torch.from_numpy(term).cuda()
+        adv = torch.empty(n, device="cuda:0"); ret = torch.empty(n, device="cuda:0")
+        talos.lib.talos_gae(ctx.handle, talos.ptr(d_r), talos.ptr(d_v), talos.ptr(d_t), n, 0.99, 0.95, 0.0, 1.0, talos.ptr(adv), talos.ptr(ret))
+        ctx.synchronize()
+        assert rel_err(adv, adv_ref) <= 1e-5 and rel_err(ret, ret_ref) <= 1e-5
+    talos.lib.talos_gae(ctx.handle, None, None, None, 0, 0.99, 0.95, 0.0, 1.0, None, None)                       # empty rollout: nothing to do
+    # buffers that start one element into an allocation: not 16-byte aligned, the element-wise load path
+    n = 4500; r = orc.f32r(orc.rng_normal(75, (n,))); v = orc.f32r(orc.rng_normal(76, (n,))); term = (orc.rng_bounded(77, n, 9) == 0).astype(np.int32)
+    adv_ref, ret_ref = orc.gae(r, v, term, 0.25, 2.0)
+    pad = lambda a, dt: torch.cat([torch.zeros(1, dtype=dt), torch.from_numpy(a).to(dt)]).cuda()[1:]
+    d_r, d_v, d_t = pad(r, torch.float32), pad(v, torch.float32), pad(term, torch.int32)
+    adv = torch.empty(n + 1, device="cuda:0")[1:]; ret = torch.empty(n + 1, device="cuda:0")[1:]
+    talos.lib.talos_gae(ctx.handle, talos.ptr(d_r), talos.ptr(d_v), talos.ptr(d_t), n, 0.99, 0.95, 0.25, 2.0, talos.ptr(adv), talos.ptr(ret))
+    out = torch.empty(n + 1, device="cuda:0")[1:]
+    talos.lib.talos_normalize_slice(ctx.handle, talos.ptr(adv), n, talos.ptr(out), None)
+    ctx.synchronize()
+    assert rel_err(adv, adv_ref) <= 1e-5 and rel_err(ret, ret_ref) <= 1e-5
+    m = orc.sum_f64(adv_ref) / n; sd = math.sqrt(orc.sum_sq_diff(adv_ref, m) / n) + 1e-8
+    assert rel_err(out, orc.normalize_slice(adv_ref, m, sd)) <= 1e-5
+
+
 def test_layout_ops(talos, ctx):
     import ctypes as C
     import torch

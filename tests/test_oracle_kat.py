@@ -187,3 +187,29 @@ def test_kv_cache_prune():
         kv.k[h] = np.arange(5 * 32, dtype=float); kv.v[h] = np.arange(5 * 16, dtype=float)
     om.prune_kv_cache(kv, cfg, 3)
     assert kv.k[0].size == 3 * 32 and kv.k[0][0] == 64.0 and kv.v[0].size == 3 * 16 and kv.v[0][0] == 32.0
+
+
+def test_gae_hand_computed_three_steps():
+    # src/ppo.rs:650-671 on a three-step buffer whose middle step ends an episode, against the formulas written out
+    r = np.array([1.0, 2.0, -1.0]); v = np.array([0.5, 0.25, 0.125]); term = np.array([0, 1, 0])
+    adv, ret = orc.gae(r, v, term, 0.0, 1.0)
+    d = 1.0 + 1e-8
+    g2 = -1.0 / d + 0.0 - 0.125                      # last step: V[len] = 0
+    g1 = 2.0 / d - 0.25                              # terminal: no bootstrap, no carry from g2
+    g0 = 1.0 / d + 0.99 * 0.25 - 0.5 + 0.99 * 0.95 * g1
+    assert np.allclose(adv, [g0, g1, g2], rtol=0, atol=1e-15) and np.allclose(ret, adv + v, rtol=0, atol=1e-15)
+    adv_c, _ = orc.gae(np.array([1000.0, -1000.0]), np.zeros(2), np.array([1, 1]), 0.0, 1.0)
+    assert adv_c.tolist() == [10.0, -10.0]           # normalised rewards are clipped to +-10 (:655)
+
+
+def test_running_mean_std_matches_reference_formulas():
+    # src/ppo.rs:444-480: count 1e-4, mean 0, var 1; one-sample updates
+    rms = orc.RunningMeanStd()
+    count, mean, var = 1e-4, 0.0, 1.0
+    for x in (1.0, 2.0, 3.0, -4.5):
+        rms.update(x)
+        delta = x - mean; tot = count + 1.0
+        m2 = var * count + delta ** 2 * count / tot
+        mean, var, count = mean + delta / tot, m2 / tot, tot
+        assert abs(rms.mean.value - mean) < 1e-15 and abs(rms.var.value - var) < 1e-15 and rms.count.value == count
+    assert abs(rms.normalize(2.0) - (2.0 - mean) / (math.sqrt(var) + 1e-8)) < 1e-15
