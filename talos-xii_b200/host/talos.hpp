@@ -14,6 +14,8 @@
 #pragma once
 #include <cmath>
 #include <cstdint>
+#include <cstdio>
+#include <cstring>
 #include <functional>
 #include <memory>
 #include <optional>
@@ -104,6 +106,48 @@ class Tensor {
   std::vector<double> to_vec() const { std::vector<double> v(len()); check(talos_download_f64(ctx(), v.data(), d(), (int64_t)v.size())); return v; }
   std::vector<double> grad_vec() const { std::vector<double> v(len()); check(talos_download_f64(ctx(), v.data(), g(), (int64_t)v.size())); return v; }
   void set_data(const std::vector<double>& v) const { TALOS_ASSERT(v.size() == len(), "Data length must match shape"); check(talos_upload_f64(ctx(), d(), v.data(), (int64_t)v.size())); }
+  // ---- file formats of the crate, so that cached models move between the two implementations ----
+  // save_binary / from_mmap (src/autograd.rs:56-92): the data as raw little-endian f64, nothing else; the shape is
+  // supplied by the reader, which fails with "Mmap size mismatch" when the byte count does not fit it.
+  bool save_binary(const std::string& path) const {
+    std::FILE* f = std::fopen(path.c_str(), "wb"); if (!f) return false;
+    const std::vector<double> v = to_vec();
+    const bool ok = std::fwrite(v.data(), sizeof(double), v.size(), f) == v.size();
+    return std::fclose(f) == 0 && ok;
+  }
+  static Tensor from_mmap(const std::string& path, std::vector<size_t> shape) {
+    std::FILE* f = std::fopen(path.c_str(), "rb"); TALOS_ASSERT(f != nullptr, "cannot open tensor file");
+    std::vector<double> v(numel(shape) + 1);
+    const size_t got = std::fread(v.data(), sizeof(double), v.size(), f); std::fclose(f);
+    TALOS_ASSERT(got == numel(shape), "Mmap size mismatch");
+    v.resize(numel(shape));
+    return new_(v, std::move(shape));
+  }
+  // The serde layout `struct Tensor { data: Vec<f64>, shape: Vec<usize> }` (src/autograd.rs:22-50) as bincode 1.x
+  // writes it with its default options: u64 little-endian element count, the f64 values, u64 rank, u64 dimensions.
+  std::vector<uint8_t> to_bincode() const {
+    const std::vector<double> v = to_vec();
+    std::vector<uint8_t> out(8 + 8 * v.size() + 8 + 8 * shape.size());
+    uint8_t* p = out.data();
+    auto put = [&p](uint64_t x) { std::memcpy(p, &x, 8); p += 8; };
+    put(v.size()); std::memcpy(p, v.data(), 8 * v.size()); p += 8 * v.size();
+    put(shape.size()); for (size_t d : shape) put((uint64_t)d);
+    return out;
+  }
+  // Reads one tensor starting at bytes[*offset]; advances *offset past it (tensors are simply concatenated inside
+  // the structs that hold them).  Panics on a truncated buffer or a shape that does not match the data length.
+  static Tensor from_bincode(const std::vector<uint8_t>& bytes, size_t* offset) {
+    size_t o = *offset;
+    auto get = [&](uint64_t* x) { TALOS_ASSERT(o + 8 <= bytes.size(), "truncated tensor record"); std::memcpy(x, bytes.data() + o, 8); o += 8; };
+    uint64_t n = 0, rank = 0; get(&n);
+    TALOS_ASSERT(n <= (bytes.size() - o) / 8, "truncated tensor record");
+    std::vector<double> v(n); std::memcpy(v.data(), bytes.data() + o, 8 * n); o += 8 * n;
+    get(&rank); TALOS_ASSERT(rank <= 8, "tensor rank out of range");
+    std::vector<size_t> shp(rank); for (auto& d : shp) { uint64_t x; get(&x); d = (size_t)x; }
+    TALOS_ASSERT(numel(shp) == n, "Data length must match shape");
+    *offset = o;
+    return new_(v, std::move(shp));
+  }
   double item() const { TALOS_ASSERT(numel(shape) == 1, "item() needs one element"); return to_vec()[0]; }
 
   // Tensor::backward (src/autograd.rs:145-184): DFS topological order keyed on the grad buffer, root grad = 1.

@@ -2,6 +2,7 @@
 // (talos::Tensor / Module over the C ABI) on the GPU.  Each test names the Rust test it mirrors.
 #include <cmath>
 #include <cstdio>
+#include <cstring>
 #include <functional>
 #include <string>
 #include <vector>
@@ -11,6 +12,7 @@
 using namespace talos;
 static int failures = 0;
 #define EXPECT(cond) do { if (!(cond)) { std::printf("    EXPECT failed: %s (line %d)\n", #cond, __LINE__); ++failures; } } while (0)
+#define EXPECT_PANIC(expr) do { bool p_ = false; try { (void)(expr); } catch (const Panic&) { p_ = true; } if (!p_) { std::printf("    expected a panic: %s (line %d)\n", #expr, __LINE__); ++failures; } } while (0)
 static void run(const char* name, const std::function<void()>& f) {
   int before = failures;
   try { f(); } catch (const std::exception& e) { std::printf("    exception: %s\n", e.what()); ++failures; }
@@ -152,6 +154,24 @@ int main(int argc, char** argv) {
     auto got = gae_advantages(Tensor::new_(r, {4}), Tensor::new_(v, {4}), term, rn);
     const std::vector<double> ga = got.first.to_vec(), gr = got.second.to_vec();
     for (int t = 0; t < 4; ++t) { EXPECT(std::fabs(ga[t] - (adv[t] - m) / sd) < 1e-5); EXPECT(std::fabs(gr[t] - ret[t]) < 1e-5); }
+  });
+  run("autograd: save_binary / from_mmap and the serde-bincode tensor layout", [] {   // src/autograd.rs:22-92
+    Tensor t = Tensor::new_({1.0, -2.5, 3.25, 4.0, 0.5, -6.0}, {2, 3});
+    const std::string path = "/tmp/talos_tensor_io_test.bin";
+    EXPECT(t.save_binary(path));
+    Tensor back = Tensor::from_mmap(path, {3, 2});                              // the reader supplies the shape
+    EXPECT(back.to_vec() == t.to_vec() && back.shape == std::vector<size_t>({3, 2}));
+    EXPECT_PANIC(Tensor::from_mmap(path, {7}));                                 // "Mmap size mismatch"
+    std::remove(path.c_str());
+    const std::vector<uint8_t> b = t.to_bincode();
+    EXPECT(b.size() == 8 + 6 * 8 + 8 + 2 * 8);
+    const uint8_t head[8] = {6, 0, 0, 0, 0, 0, 0, 0}; EXPECT(std::memcmp(b.data(), head, 8) == 0);      // u64 LE element count
+    double first; std::memcpy(&first, b.data() + 8, 8); EXPECT(first == 1.0);
+    const uint8_t rank[8] = {2, 0, 0, 0, 0, 0, 0, 0}; EXPECT(std::memcmp(b.data() + 56, rank, 8) == 0);
+    std::vector<uint8_t> two = b; two.insert(two.end(), b.begin(), b.end());    // two tensors back to back, as inside Linear
+    size_t off = 0; Tensor a1 = Tensor::from_bincode(two, &off), a2 = Tensor::from_bincode(two, &off);
+    EXPECT(off == two.size() && a1.to_vec() == t.to_vec() && a2.shape == t.shape);
+    two.pop_back(); off = 0; Tensor::from_bincode(two, &off); EXPECT_PANIC(Tensor::from_bincode(two, &off));   // truncated second record
   });
   run("dqn: dueling network consumer (batch 64) trains", [] {            // src/dqn.rs:68-107, :207-239, :482-584
     Linear l1(8, 64, true, 1), l2(64, 64, true, 2), val(64, 1, true, 3), adv(64, 5, true, 4);
