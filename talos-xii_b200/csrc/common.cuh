@@ -134,6 +134,10 @@ void talos_gemm_fp32_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t
 bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A,
                           int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, int mode,
                           const EpiArgs& epi);
+// dZ = dY * act'(saved) (dz may alias dy) and db (+)= column sums of dZ in one pass over the rows; false when the
+// shape is not served by the vector kernel (n % 4 != 0, n > 1024 or unaligned), in which case nothing was launched.
+bool talos_dact_colsum_launch(talos_ctx* ctx, const float* dy, float* dz, const float* saved, int dact, float* db, int64_t rows, int64_t n,
+                              int accumulate);
 bool talos_gemm_tc_launch_batched(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                   int64_t strideA, const float* B, int64_t ldb, int64_t strideB, float* C, int64_t ldc, int64_t strideC,
                                   int64_t batch, int mode, const EpiArgs& epi);

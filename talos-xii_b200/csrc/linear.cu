@@ -38,11 +38,16 @@ TALOS_API talos_status talos_linear_bwd(talos_ctx* ctx, const float* x, const fl
   if (rows == 0) return TALOS_OK;
   TALOS_REQUIRE(dy && W && (x || !dW), TALOS_ERR_ARG, "null pointer");
   const float* dz = dy;
+  bool db_done = false;
   if (act != TALOS_ACT_NONE) {
     TALOS_REQUIRE(saved != nullptr, TALOS_ERR_ARG, "activation backward needs the saved tensor");
     float* buf = (float*)talos_workspace2(ctx, sizeof(float) * (size_t)(rows * out_f));
-    dact_mul_kernel<<<(unsigned)ceil_div(rows * out_f, 256), 256, 0, ctx->stream>>>(dy, saved, buf, rows * out_f, act);
-    talos_launched(ctx, "dact_mul");
+    // dZ = dY * act'(saved); when the bias gradient is wanted too, the same pass produces its column sums
+    if (db && talos_dact_colsum_launch(ctx, dy, buf, saved, act, db, rows, out_f, (accumulate >> 2) & 1)) db_done = true;
+    else {
+      dact_mul_kernel<<<(unsigned)ceil_div(rows * out_f, 256), 256, 0, ctx->stream>>>(dy, saved, buf, rows * out_f, act);
+      talos_launched(ctx, "dact_mul");
+    }
     dz = buf;
   }
   if (dx) {   // dL/dx (+)= dZ . W^T   (src/autograd.rs:275-308)
@@ -53,7 +58,7 @@ TALOS_API talos_status talos_linear_bwd(talos_ctx* ctx, const float* x, const fl
     EpiArgs e{nullptr, nullptr, 0, nullptr, 0, 0, 0, (accumulate >> 1) & 1};
     gemm_any(ctx, TALOS_OP_T, TALOS_OP_N, in_f, out_f, rows, x, in_f, dz, out_f, dW, out_f, mode, e);
   }
-  if (db) {   // dL/db (+)= column sums of dZ   (src/autograd.rs:539-543)
+  if (db && !db_done) {   // dL/db (+)= column sums of dZ   (src/autograd.rs:539-543)
     talos_status st = talos_colsum(ctx, dz, db, rows, out_f, (accumulate >> 2) & 1);
     if (st) return st;
   }

@@ -109,16 +109,27 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   // heads: dWh = h2^T.dz ; dbh = colsum(dz) ; dh2 = (dz.Wh^T) * (1 - h2^2)
   gemm(ctx, 1, 0, H, HP, n, p->h2, H, p->dz, HP, G + p->o_wh, HP, c.mode, none);
   if ((st = talos_colsum(ctx, p->dz, G + p->o_bh, n, HP, 0))) throw talos_error(st, talos_last_error_string());
-  EpiArgs d2{nullptr, nullptr, 0, p->h2, H, 0, TALOS_ACT_TANH, 0};
-  gemm(ctx, 0, 1, n, H, HP, p->dz, HP, P + p->o_wh, HP, p->dh2, H, c.mode, d2);
+  // dH = (dZ_next . W^T) * tanh'(h), db = colsum(dH).  The tanh' factor is not fused into the GEMM's epilogue when
+  // the streaming kernel can take it: that epilogue reads the saved activation row by row and is what bounds these
+  // skinny GEMMs (72 -> ~30 us at K = 32); one streaming pass applies the factor in place and produces the bias
+  // gradient's column sums at the same time.
+  auto backprop_hidden = [&](const float* dz_next, int64_t k, const float* W, float* dh, const float* h_saved, float* db) {
+    if (H % 4 == 0 && H <= 1024) {                                              // what the streaming kernel takes (buffers are aligned)
+      gemm(ctx, 0, 1, n, H, k, dz_next, k, W, k, dh, H, c.mode, none);
+      if (!talos_dact_colsum_launch(ctx, dh, dh, h_saved, TALOS_ACT_TANH, db, n, H, 0)) throw talos_error(TALOS_ERR_CUDA, "dact + colsum kernel refused an aligned shape");
+      return;
+    }
+    EpiArgs d{nullptr, nullptr, 0, h_saved, H, 0, TALOS_ACT_TANH, 0};
+    gemm(ctx, 0, 1, n, H, k, dz_next, k, W, k, dh, H, c.mode, d);
+    talos_status s2 = talos_colsum(ctx, dh, db, n, H, 0);
+    if (s2) throw talos_error(s2, talos_last_error_string());
+  };
+  backprop_hidden(p->dz, HP, P + p->o_wh, p->dh2, p->h2, G + p->o_b2);
   // layer 2
   gemm(ctx, 1, 0, H, H, n, p->h1, H, p->dh2, H, G + p->o_w2, H, c.mode, none);
-  if ((st = talos_colsum(ctx, p->dh2, G + p->o_b2, n, H, 0))) throw talos_error(st, talos_last_error_string());
-  EpiArgs d1{nullptr, nullptr, 0, p->h1, H, 0, TALOS_ACT_TANH, 0};
-  gemm(ctx, 0, 1, n, H, H, p->dh2, H, P + p->o_w2, H, p->dh1, H, c.mode, d1);
+  backprop_hidden(p->dh2, H, P + p->o_w2, p->dh1, p->h1, G + p->o_b1);
   // layer 1 (no gradient w.r.t. the observations)
   gemm(ctx, 1, 0, c.obs_dim, H, n, obs, c.obs_dim, p->dh1, H, G + p->o_w1, H, c.mode, none);
-  if ((st = talos_colsum(ctx, p->dh1, G + p->o_b1, n, H, 0))) throw talos_error(st, talos_last_error_string());
   if (comm) { if ((st = talos_comm_allreduce_sum(comm, G, p->n_int + 4))) throw talos_error(st, talos_last_error_string()); }
   p->t += 1;
   float* stat_slot = p->step_stats + 4 * (p->steps_in_epoch % MAX_STEPS_PER_EPOCH);

@@ -194,8 +194,11 @@ __global__ void colsum_stage1_kernel(const float* __restrict__ g, long long rows
 
 // Stage 1 for n % 4 == 0 and n <= 1024: 256 threads = (n/4 float4 columns) x (row lanes); every thread
 // streams its rows with eight 128-bit loads in flight; row lanes are combined in lane order.
+// DACT != 0 fuses the activation derivative of a Linear backward into the same pass: g_out = g * act'(saved)
+// (g_out may be g) and the column sums are those of the product (dZ = dY * act'(.), db = colsum(dZ)).
+template <int DACT>
 __global__ void __launch_bounds__(256)
-colsum_stage1_vec_kernel(const float4* __restrict__ g, long long rows, int n4, long long rows_per_cta,
+colsum_stage1_vec_kernel(const float4* g, float4* g_out, const float4* __restrict__ saved, long long rows, int n4, long long rows_per_cta,
                          float* __restrict__ partial) {
   extern __shared__ float4 shv[];                       // [row_lanes][n4]
   const int row_lanes = 256 / n4;
@@ -205,7 +208,12 @@ colsum_stage1_vec_kernel(const float4* __restrict__ g, long long rows, int n4, l
   if (rl < row_lanes) {
 #pragma unroll 8
     for (long long r = r0 + rl; r < r1; r += row_lanes) {
-      const float4 v = __ldcs(g + r * n4 + cl);
+      float4 v = __ldcs(g + r * n4 + cl);
+      if (DACT) {
+        const float4 a = __ldcs(saved + r * n4 + cl);
+        v.x *= talos_dact(a.x, DACT); v.y *= talos_dact(a.y, DACT); v.z *= talos_dact(a.z, DACT); v.w *= talos_dact(a.w, DACT);
+        g_out[r * n4 + cl] = v;
+      }
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
     shv[rl * n4 + cl] = s;
@@ -431,27 +439,44 @@ TALOS_API talos_status talos_rmsnorm_bwd(talos_ctx* ctx, const float* dy, const 
   TALOS_ENTRY_END
 }
 
+// out[c] (+)= sum_r g[r][c]; with dact != 0 the summand is g_out[r][c] = g[r][c] * act'(saved[r][c]), also written
+// (vector path only: n % 4 == 0, n <= 1024, 16-byte aligned; returns false when the shape needs the plain path).
+static bool colsum_vec_launch(talos_ctx* ctx, const float* g, float* g_out, const float* saved, int dact, float* out, int64_t rows, int64_t n, int accumulate) {
+  const bool vec = (n % 4 == 0) && n <= 1024 && aligned16(g) && (!dact || (aligned16(saved) && aligned16(g_out)));
+  if (!vec) return false;
+  const int n4 = (int)(n / 4);
+  int64_t slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 32), 4 * (int64_t)ctx->sm_count));
+  int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
+  float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
+  size_t shmem = sizeof(float4) * (size_t)(256 / n4) * n4;
+  auto G4 = (const float4*)g; auto O4 = (float4*)g_out; auto S4 = (const float4*)saved;
+  switch (dact) {
+    case 0: colsum_stage1_vec_kernel<0><<<(unsigned)slabs, 256, shmem, ctx->stream>>>(G4, O4, S4, rows, n4, rows_per, partial); break;
+    case TALOS_ACT_RELU: colsum_stage1_vec_kernel<TALOS_ACT_RELU><<<(unsigned)slabs, 256, shmem, ctx->stream>>>(G4, O4, S4, rows, n4, rows_per, partial); break;
+    case TALOS_ACT_TANH: colsum_stage1_vec_kernel<TALOS_ACT_TANH><<<(unsigned)slabs, 256, shmem, ctx->stream>>>(G4, O4, S4, rows, n4, rows_per, partial); break;
+    case TALOS_ACT_SILU: colsum_stage1_vec_kernel<TALOS_ACT_SILU><<<(unsigned)slabs, 256, shmem, ctx->stream>>>(G4, O4, S4, rows, n4, rows_per, partial); break;
+    default: throw talos_error(TALOS_ERR_ARG, "bad activation kind");
+  }
+  talos_launched(ctx, "colsum_stage1");
+  colsum_partials_kernel<<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
+  talos_launched(ctx, "colsum_stage2");
+  return true;
+}
+
+// Internal (Linear backward, PPO trainer): dZ = dY * act'(saved) (dz may be dy), db (+)= colsum(dZ) in one pass.
+bool talos_dact_colsum_launch(talos_ctx* ctx, const float* dy, float* dz, const float* saved, int dact, float* db, int64_t rows, int64_t n,
+                              int accumulate) {
+  return colsum_vec_launch(ctx, dy, dz, saved, dact, db, rows, n, accumulate);
+}
+
 TALOS_API talos_status talos_colsum(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n, int32_t accumulate) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
   TALOS_REQUIRE(rows >= 0 && n > 0 && n < (1 << 24), TALOS_ERR_SHAPE, "bad colsum shape");
   TALOS_REQUIRE(g && out, TALOS_ERR_ARG, "null pointer");
-  const bool vec = (n % 4 == 0) && n <= 1024 && aligned16(g) && (256 % (n / 4) == 0 || n / 4 <= 256);
-  int64_t slabs;
-  if (vec && 256 / (n / 4) >= 1) {
-    const int n4 = (int)(n / 4);
-    slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 32), 4 * (int64_t)ctx->sm_count));
-    int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
-    float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
-    size_t shmem = sizeof(float4) * (size_t)(256 / n4) * n4;
-    colsum_stage1_vec_kernel<<<(unsigned)slabs, 256, shmem, ctx->stream>>>((const float4*)g, rows, n4, rows_per, partial);
-    talos_launched(ctx, "colsum_stage1");
-    colsum_partials_kernel<<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
-    talos_launched(ctx, "colsum_stage2");
-    return TALOS_OK;
-  }
+  if (colsum_vec_launch(ctx, g, nullptr, nullptr, 0, out, rows, n, accumulate)) return TALOS_OK;
   int64_t col_blocks = ceil_div(n, 128);
-  slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 64), (4 * (int64_t)ctx->sm_count) / col_blocks + 1));
+  int64_t slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 64), (4 * (int64_t)ctx->sm_count) / col_blocks + 1));
   int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
   float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
   colsum_stage1_kernel<<<dim3((unsigned)col_blocks, (unsigned)slabs), 128, 0, ctx->stream>>>(g, rows, (int)n, rows_per, partial);
