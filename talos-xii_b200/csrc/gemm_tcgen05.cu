@@ -32,12 +32,22 @@ namespace {
 // BPS (3xTF32 only): the B operand arrives already split into TF32 hi / lo matrices (two tensor maps), so the
 // converter warps only split A.  Used when B is small (weights): it is then split once per call instead of once
 // per output tile.
+// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, then the epilogue warps, then (3xTF32) the converter
+// warps.  When both operands are split in the kernel (no pre-split B: the weight-gradient products, whose epilogue
+// runs once per 16 k-blocks) the converter is the busy role, so it gets eight warps and the epilogue four.
+template <bool X3, bool BPS> struct TcRoles {
+  static constexpr int EPI_WARPS = (X3 && !BPS) ? 4 : 8;
+  static constexpr int CONV_WARPS = X3 ? (BPS ? 4 : 8) : 0;
+  static constexpr int THREADS = (2 + EPI_WARPS + CONV_WARPS) * 32;       // 448 (3xTF32) or 320 (TF32)
+};
+
 template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false>
-__global__ void __launch_bounds__(X3 ? 448 : 320, MINB)
+__global__ void __launch_bounds__((TcRoles<X3, BPS>::THREADS), MINB)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, TcArgs g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
+  constexpr int EPI_WARPS = TcRoles<X3, BPS>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS>::CONV_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
@@ -56,8 +66,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, 4); mbar_init(empty + s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 8); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, CONV_WARPS ? CONV_WARPS : 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, EPI_WARPS); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -138,16 +148,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         acc_phase[acc] ^= 1; acc ^= 1;
       }
     }
-  } else if (warp < 10) {
-    // ------------------------------------------------------------- epilogue: 8 warps, two per TMEM lane quadrant, each
-    // taking half of the tile's columns.  The epilogue is latency-bound per warp, so it needs the extra warps.
+  } else if (warp < 2 + EPI_WARPS) {
+    // ------------------------------------------------------------- epilogue: normally 8 warps, two per TMEM lane quadrant,
+    // each taking half of the tile's columns (the epilogue is latency-bound per warp, so it needs the extra warps).
     int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int bz = it / per_batch, r = it - bz * per_batch;
       const int ks = r / tiles_mn, rem = r % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
       if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
       tc_fence_after();
-      tc_epilogue_tile<BN>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32), (long long)mb * BM, nb, ks, bz, store_count);
+      tc_epilogue_tile<BN, EPI_WARPS>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32), (long long)mb * BM, nb, ks, bz, store_count);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + acc);
@@ -156,8 +166,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (lane == 0) tma_store_wait_read<0>();                 // shared memory must outlive the stores that read it
     __syncwarp();
   } else if (X3) {
-    // ------------------------------------------------------------- converter (4 warps): fp32 -> (hi, lo) TF32 pair
-    const int ct = threadIdx.x - 320;                          // 0..127
+    // ------------------------------------------------------------- converter warps: fp32 -> (hi, lo) TF32 pair
+    constexpr int CONV_THREADS = (CONV_WARPS ? CONV_WARPS : 1) * 32;
+    const int ct = threadIdx.x - (2 + EPI_WARPS) * 32;         // 0 .. CONV_THREADS-1
     int stage = 0; uint32_t phase = 0; bool ok = true;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int ks = (it % per_batch) / tiles_mn;
@@ -167,10 +178,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // The split is elementwise, so it is oblivious to the swizzle: same offset in, same offset out.
         float4* ahi = (float4*)(sA + stage * A_BYTES); float4* alo = (float4*)(sAlo + stage * A_BYTES);
         float4* bhi = (float4*)(sB + stage * B_BYTES); float4* blo = (float4*)(sBlo + stage * B_BYTES);
-        constexpr int CONV_ITERS = (A_BYTES + (BPS ? 0 : B_BYTES)) / 16 / 128;
+        constexpr int CONV_ITERS = (A_BYTES + (BPS ? 0 : B_BYTES)) / 16 / CONV_THREADS;
+        static_assert((A_BYTES + (BPS ? 0 : B_BYTES)) % (16 * CONV_THREADS) == 0, "tile bytes must divide evenly over the converter threads");
 #pragma unroll 8
         for (int ci = 0; ci < CONV_ITERS; ++ci) {
-          const int i = ct + ci * 128;
+          const int i = ct + ci * CONV_THREADS;
           float4* hi = i < A_BYTES / 16 ? ahi + i : bhi + (i - A_BYTES / 16);
           float4* lo = i < A_BYTES / 16 ? alo + i : blo + (i - A_BYTES / 16);
           float4 v = *hi, h, l;
@@ -280,7 +292,7 @@ void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, co
   auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS>;
   size_t smem = tc_smem_bytes<BN, STAGES, X3>();
   TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, X3 ? 448 : 320, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
+  kern<<<grid, TcRoles<X3, BPS>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
   talos_launched(ctx, "gemm_tcgen05");
 }
 

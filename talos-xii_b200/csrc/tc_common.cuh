@@ -184,16 +184,17 @@ __device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restri
 // One epilogue warp's share of a finished 128 x BN accumulator: warp w (2..9) owns TMEM lane quadrant w%4 (32 rows,
 // one per lane) and half of the columns, drained 32 columns at a time.  `t_base` is the TMEM address of the
 // accumulator's first column, `m_base` the global row of TMEM lane 0, `stage` this warp's 4 KB staging buffer.
-template <int BN>
+template <int BN, int EPI_WARPS = 8>
 __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensorMap* tmap_c, uint32_t t_base, int warp, int lane, float* stage,
                                                  long long m_base, int nb, int ks, int bz, uint32_t& store_count) {
+  static_assert(EPI_WARPS == 8 || EPI_WARPS == 4, "two warps per TMEM lane quadrant, or one");
   float* const c_base = g.C + (long long)bz * g.stride_c;   // this batch member's C (split-K never batches: ks or bz is 0)
   // Each warp drains its 32-lane quadrant (one accumulator row per lane) 32 columns at a time.
-  const int quad = warp & 3, half = (warp - 2) >> 2;
+  const int quad = warp & 3, half = EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;
   const long long m0 = m_base + quad * 32;
   const uint32_t t_row = t_base + ((uint32_t)(quad * 32) << 16);
   const int rows_valid = (int)min((long long)32, (long long)g.M - m0);
-  constexpr int HALF_COLS = BN >= 64 ? BN / 2 : BN;
+  constexpr int HALF_COLS = (EPI_WARPS == 8 && BN >= 64) ? BN / 2 : BN;
 #pragma unroll 1
   for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 32) {
     const long long n0 = (long long)nb * BN + c0;
