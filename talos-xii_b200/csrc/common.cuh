@@ -77,14 +77,14 @@ inline void talos_launched(talos_ctx* ctx, const char* what) {
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // ---- activation helpers shared by the GEMM epilogues and the elementwise kernels ----
-// Branch-free tanh with |abs error| < 2e-7: x - x^3/3 + 2x^5/15 below 0.06 (no cancellation there),
-// 1 - 2/(e^{2|x|}+1) elsewhere with the hardware exp2 / reciprocal approximations.
+// tanh(x) = 1 - 2 / (2^(2x log2 e) + 1) with the hardware exp2 / reciprocal approximations: five dependent
+// instructions, no branch, correct limits (+-1) without clamping, |abs error| < 3e-7 (the GEMM epilogues are
+// instruction-latency bound, so the short chain matters more than the last bit near zero, where the RELATIVE
+// error of this form grows as 1e-7 / |x|).
 __device__ __forceinline__ float talos_tanh(float x) {
-  const float ax = fabsf(x), x2 = x * x;
-  const float poly = x * (1.f + x2 * (-0.33333334f + x2 * 0.13333334f));
-  const float e = __expf(2.f * ax);
-  const float t = copysignf(1.f - __fdividef(2.f, e + 1.f), x);
-  return ax < 0.06f ? poly : t;
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));   // exp(2x) = 2^(2x log2 e)
+  return 1.f - __fdividef(2.f, e + 1.f);                                         // 2/inf = 0 and 2/1 give the +-1 limits
 }
 __device__ __forceinline__ float talos_act(float v, int act) {
   switch (act) {
