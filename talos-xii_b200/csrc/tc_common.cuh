@@ -149,7 +149,9 @@ __device__ __forceinline__ void epilogue_rows_t(const EpiArgs& e, const float* s
     C[m * ldc + n] = v;
   }
 }
-__device__ __noinline__ void epilogue_rows(const EpiArgs& e, const float* stage, int lane, long long m0, int rows_valid, long long n,
+// (EpiArgs by value: a reference would force the kernel's whole argument struct out of the constant bank into a
+// local-memory copy, and every field read of every epilogue chunk with it.)
+__device__ __noinline__ void epilogue_rows(const EpiArgs e, const float* stage, int lane, long long m0, int rows_valid, long long n,
                                            bool col_ok, float* C, long long ldc) {
   const int dact = e.aux_in ? e.dact : 0;
   switch (e.act * 4 + dact) {
