@@ -202,6 +202,23 @@ talos_status talos_gae(talos_ctx* ctx, const float* rewards, const float* values
  * the mean and that denominator.  y may alias x. */
 talos_status talos_normalize_slice(talos_ctx* ctx, const float* x, int64_t n, float* y, float* stats);
 
+/* ---- dueling double-DQN train step (src/dqn.rs) --------------------------------------------- */
+/* DuelingQNetwork::forward_impl, batch branch (src/dqn.rs:76-93): q = v + adv - mean_a(adv), which the
+ * crate spells as three matmuls with constant ones matrices.  v [B,1], adv [B,A], q [B,A]. */
+talos_status talos_dueling_combine_fwd(talos_ctx* ctx, const float* v, const float* adv, float* q, int64_t B, int64_t A);
+/* Its backward: dv[b] (+)= sum_a dq[b,a]; dadv[b,a] (+)= dq[b,a] - mean_a dq[b,:].  dv or dadv may be null. */
+talos_status talos_dueling_combine_bwd(talos_ctx* ctx, const float* dq, float* dv, float* dadv, int64_t B, int64_t A, int32_t accumulate);
+/* Double-DQN targets (src/dqn.rs:524-556): target[b] = r[b] + gamma * q_next_target[b, argmax_a q_next_eval[b,a]] * (1 - done[b]);
+ * the first maximum wins (strict >, as the crate's loop).  dones holds 0.0 / 1.0. */
+talos_status talos_dqn_target(talos_ctx* ctx, const float* q_next_eval, const float* q_next_target, const float* rewards,
+                              const float* dones, float gamma, float* target, int64_t B, int64_t A);
+/* q_sel[b] = q[b, actions[b]] (the mask product + matmul with ones, src/dqn.rs:516-520); loss[0] = mean_b (q_sel - target)^2
+ * (mse_loss, src/autograd.rs:1599-1603); dq (nullable) [B,A] is OVERWRITTEN with dloss/dq. */
+talos_status talos_dqn_loss_fwd_bwd(talos_ctx* ctx, const float* q, const int32_t* actions, const float* target, float* loss,
+                                    float* dq, int64_t B, int64_t A);
+/* DuelingQNetwork::soft_update (src/dqn.rs:129-150): target = target * (1 - tau) + source * tau over n parameters. */
+talos_status talos_soft_update(talos_ctx* ctx, float* target_params, const float* source_params, float tau, int64_t n);
+
 /* ---- batched rollout inference ------------------------------------------------------------ */
 /* One decode step of MultiHeadLatentAttention::forward_inference_cached (src/transformer.rs:688-841)
  * for N independent simulations at once -- the attention part of ActorCritic::step_inference_cached

@@ -324,6 +324,47 @@ def rollout_reference(ac, states, resets, context_len):
         out.append(row)
     return np.array(out)
 
+# ------------------------------------------------------------------ dueling double-DQN pieces (src/dqn.rs)
+
+
+def dueling_combine(v, adv):
+    """DuelingQNetwork::forward_impl, batch branch (src/dqn.rs:76-93): val.ones(1,A) + adv - (adv.ones(A,1)/A).ones(1,A)."""
+    A = adv.shape[1]
+    return v.reshape(-1, 1) @ np.ones((1, A)) + adv - (adv @ np.full((A, 1), 1.0 / A)) @ np.ones((1, A))
+
+
+def dueling_combine_bwd(dq):
+    """Backward of the three matmuls: dv = dq.ones(A,1); dadv = dq - (dq.ones(A,1)).(ones(1,A)/A)."""
+    A = dq.shape[1]
+    dv = dq @ np.ones((A, 1))
+    return dv, dq - dv @ np.full((1, A), 1.0 / A)
+
+
+def dqn_target(q_next_eval, q_next_target, rewards, dones, gamma=0.99):
+    """src/dqn.rs:524-556: argmax (first maximum) from the online network, value from the target network."""
+    out = np.empty(len(rewards))
+    for i in range(len(rewards)):
+        best, mx = 0, -np.inf
+        for k, val in enumerate(q_next_eval[i]):
+            if val > mx:
+                mx, best = val, k
+        out[i] = rewards[i] + gamma * q_next_target[i, best] * (1.0 - dones[i])
+    return out
+
+
+def dqn_loss_fwd_bwd(q, actions, target):
+    """(q * mask).ones(A,1) then mse_loss (src/dqn.rs:516-561, src/autograd.rs:1599-1603) and its gradient w.r.t. q."""
+    B = q.shape[0]
+    sel = q[np.arange(B), actions]
+    d = sel - target
+    dq = np.zeros_like(q); dq[np.arange(B), actions] = 2.0 * d / B
+    return float(np.mean(d * d)), dq
+
+
+def soft_update(target, source, tau):
+    """src/dqn.rs:129-150."""
+    return target * (1.0 - tau) + source * tau
+
 # ------------------------------------------------------------------ plain multi-head block (BASELINE config 3) -- extension
 
 

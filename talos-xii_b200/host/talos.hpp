@@ -565,6 +565,66 @@ struct ActorCritic {                                                            
   std::vector<Tensor> parameters() const { auto p = backbone.parameters(); for (auto& t : actor_head.parameters()) p.push_back(t); for (auto& t : critic_head.parameters()) p.push_back(t); return p; }
 };
 
+// DuelingQNetwork (src/dqn.rs:46-160): 8 -> 64 -> 64 -> {value 1, advantage 5}, ReLU, Q = V + A - mean(A).
+// The crate spells the combination as three matmuls with constant ones matrices; here it is one fused tape node.
+struct DuelingQNetwork : Module {
+  static constexpr size_t DIM = 8, ACTION_SPACE = 5;
+  Linear l1, l2, val_head, adv_head;
+  explicit DuelingQNetwork(uint64_t seed) : l1(DIM, 64, true, seed), l2(64, 64, true, seed + 1), val_head(64, 1, true, seed + 2), adv_head(64, ACTION_SPACE, true, seed + 3) {}   // :55-58
+  Tensor forward(const Tensor& state) const override {                              // forward_impl :68-107 (both branches compute the same thing)
+    const bool single = state.shape.size() == 1;
+    Tensor s2 = single ? state.reshape({1, state.shape[0]}) : state;
+    Tensor x = l2.forward_act(l1.forward_act(s2, TALOS_ACT_RELU), TALOS_ACT_RELU);
+    Tensor val = val_head.forward(x), adv = adv_head.forward(x);
+    const size_t B = adv.shape[0], A = adv.shape[1];
+    Tensor q = Tensor::result({B, A}, {val, adv}, [B, A](const Tensor& o, const std::vector<Tensor>& p) {
+      check(talos_dueling_combine_bwd(ctx(), o.g(), p[0].g(), p[1].g(), (int64_t)B, (int64_t)A, 1));
+    });
+    check(talos_dueling_combine_fwd(ctx(), val.d(), adv.d(), q.d(), (int64_t)B, (int64_t)A));
+    return single ? q.reshape({A}) : q;
+  }
+  std::vector<Tensor> parameters() const override {
+    std::vector<Tensor> p; for (const Linear* l : {&l1, &l2, &val_head, &adv_head}) for (auto& t : l->parameters()) p.push_back(t); return p;
+  }
+  void load_state_dict(const DuelingQNetwork& other) {                              // :112-127
+    auto a = parameters(), b = other.parameters();
+    for (size_t i = 0; i < a.size(); ++i) check(talos_copy_device(ctx(), a[i].d(), b[i].d(), sizeof(float) * a[i].len()));
+  }
+  void soft_update(const DuelingQNetwork& source, double tau) {                     // :129-150
+    auto a = parameters(), b = source.parameters();
+    for (size_t i = 0; i < a.size(); ++i) check(talos_soft_update(ctx(), a[i].d(), b[i].d(), (float)tau, (int64_t)a[i].len()));
+  }
+  size_t predict_action(const Tensor& state) const {                                // :152-170: first maximum
+    const std::vector<double> q = forward(state).to_vec();
+    size_t best = 0; double mx = -INFINITY;
+    for (size_t i = 0; i < q.size(); ++i) if (q[i] > mx) { mx = q[i]; best = i; }
+    return best;
+  }
+};
+
+// The loss of one DQN train step (src/dqn.rs:516-561) as a tape node on the policy network's Q values: double-DQN
+// targets from the two networks' next-state Q values, Q of the taken actions, mean squared error.
+inline Tensor dqn_loss(const Tensor& q, const std::vector<int32_t>& actions, const Tensor& q_next_eval, const Tensor& q_next_target,
+                       const std::vector<double>& rewards, const std::vector<double>& dones, double gamma = 0.99) {
+  const size_t B = q.shape[0], A = q.shape[1];
+  TALOS_ASSERT(actions.size() == B && rewards.size() == B && dones.size() == B && q_next_eval.len() == B * A && q_next_target.len() == B * A, "DQN batch size mismatch");
+  Tensor r = Tensor::new_(rewards, {B}), d = Tensor::new_(dones, {B}), target = Tensor::zeros({B});
+  Buf act = make_buf(B, false), dq = make_buf(B * A, false);
+  check(talos_copy_from_host(ctx(), act->dev, actions.data(), sizeof(int32_t) * B));
+  check(talos_dqn_target(ctx(), q_next_eval.d(), q_next_target.d(), r.d(), d.d(), (float)gamma, target.d(), (int64_t)B, (int64_t)A));
+  Tensor loss = Tensor::result({1}, {q}, [dq, B, A](const Tensor& o, const std::vector<Tensor>& p) {
+    // dq holds dloss/dq for an upstream gradient of 1; scale by the actual one (1.0 when loss.backward() starts here)
+    Buf scaled = make_buf(B * A, false);
+    check(talos_fill_from_scalar(ctx(), o.g(), 1.f, scaled->dev, (int64_t)(B * A), 0));
+    check(talos_eltwise_binary(ctx(), TALOS_EW_MUL, scaled->dev, dq->dev, scaled->dev, (int64_t)(B * A)));
+    check(talos_eltwise_binary(ctx(), TALOS_EW_ADD, p[0].g(), scaled->dev, p[0].g(), (int64_t)(B * A)));
+    Runtime::get().synchronize();
+  });
+  check(talos_dqn_loss_fwd_bwd(ctx(), q.d(), (const int32_t*)act->dev, target.d(), loss.d(), dq->dev, (int64_t)B, (int64_t)A));
+  Runtime::get().synchronize();                                                     // `act`, r, d are released at scope exit
+  return loss;
+}
+
 // RunningMeanStd (src/ppo.rs:444-480): host arithmetic in f64 exactly as the crate (a few scalars per reward).
 struct RunningMeanStd {
   double count = 1e-4, mean = 0.0, var = 1.0;

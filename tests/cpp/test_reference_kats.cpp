@@ -1,5 +1,6 @@
 // The reference crate's own unit tests for this path, replayed through the C++ host mirror
 // (talos::Tensor / Module over the C ABI) on the GPU.  Each test names the Rust test it mirrors.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -172,6 +173,40 @@ int main(int argc, char** argv) {
     size_t off = 0; Tensor a1 = Tensor::from_bincode(two, &off), a2 = Tensor::from_bincode(two, &off);
     EXPECT(off == two.size() && a1.to_vec() == t.to_vec() && a2.shape == t.shape);
     two.pop_back(); off = 0; Tensor::from_bincode(two, &off); EXPECT_PANIC(Tensor::from_bincode(two, &off));   // truncated second record
+  });
+  run("dqn: DuelingQNetwork mirror, double-DQN loss, soft update", [] {     // src/dqn.rs:46-160, :482-584
+    DuelingQNetwork policy(7), target(7);
+    Tensor states = Tensor::rand({64, 8}, -1.0, 1.0, 9), next = Tensor::rand({64, 8}, -1.0, 1.0, 11);
+    // the fused combination equals the crate's three-matmul spelling
+    Tensor x = policy.l2.forward(policy.l1.forward(states).relu()).relu();
+    Tensor v = policy.val_head.forward(x), a = policy.adv_head.forward(x);
+    Tensor ones15 = Tensor::new_(std::vector<double>(5, 1.0), {1, 5}), fifth = Tensor::new_(std::vector<double>(5, 0.2), {5, 1});
+    const std::vector<double> spelled = (v.matmul(ones15) + a - a.matmul(fifth).matmul(ones15)).to_vec(), fused = policy.forward(states).to_vec();
+    double worst = 0; for (size_t i = 0; i < fused.size(); ++i) worst = std::max(worst, std::fabs(fused[i] - spelled[i]));
+    EXPECT(worst < 1e-5);
+    EXPECT(policy.forward(Tensor::rand({8}, -1.0, 1.0, 3)).shape == std::vector<size_t>({5}));    // single-state branch
+    std::vector<int32_t> actions(64); std::vector<double> rewards(64), dones(64);
+    for (int i = 0; i < 64; ++i) { actions[i] = i % 5; rewards[i] = 0.1 * (i % 7) - 0.3; dones[i] = (i % 9 == 0) ? 1.0 : 0.0; }
+    std::vector<Tensor> params = policy.parameters();
+    Adam opt(params, 1e-3); opt.clip_norm = 1.0;                                                 // src/dqn.rs:207-239
+    double first = 0, last = 0;
+    for (int it = 0; it < 40; ++it) {
+      opt.zero_grad();
+      Tensor loss = dqn_loss(policy.forward(states), actions, policy.forward(next), target.forward(next), rewards, dones);
+      loss.backward(); opt.step();
+      target.soft_update(policy, 0.005);
+      if (it == 0) first = loss.item();
+      last = loss.item();
+    }
+    EXPECT(std::isfinite(last) && last < first);
+    // (with the crate's half-range LCG every weight is negative, so the second ReLU layer is dead and only the head
+    //  biases learn: they are what the soft update has to track)
+    const std::vector<double> tw = target.val_head.bias->to_vec(), pw = policy.val_head.bias->to_vec();
+    double moved = 0, gap = 0; DuelingQNetwork fresh(7); const std::vector<double> fw = fresh.val_head.bias->to_vec();
+    for (size_t i = 0; i < tw.size(); ++i) { moved += std::fabs(tw[i] - fw[i]); gap += std::fabs(tw[i] - pw[i]); }
+    EXPECT(moved > 0 && gap > 0);                                                                // the target trails the policy
+    target.load_state_dict(policy); EXPECT(target.l2.weight.to_vec() == policy.l2.weight.to_vec());
+    EXPECT(policy.predict_action(Tensor::rand({8}, -1.0, 1.0, 5)) < 5);
   });
   run("dqn: dueling network consumer (batch 64) trains", [] {            // src/dqn.rs:68-107, :207-239, :482-584
     Linear l1(8, 64, true, 1), l2(64, 64, true, 2), val(64, 1, true, 3), adv(64, 5, true, 4);

@@ -388,6 +388,43 @@ def test_gae_and_advantage_normalisation(talos, ctx):
     assert rel_err(out, orc.normalize_slice(adv_ref, m, sd)) <= 1e-5
 
 
+def test_dqn_step_pieces(talos, ctx):
+    import torch
+    for B, A in [(64, 5), (1, 5), (1000, 3), (37, 16)]:          # 64 x 5 is the crate's batch (src/dqn.rs:34, :15)
+        v = orc.f32r(orc.rng_normal(80, (B, 1))); adv = orc.f32r(orc.rng_normal(81, (B, A)))
+        q = torch.empty(B, A, device="cuda:0")
+        talos.lib.talos_dueling_combine_fwd(ctx.handle, dptr(talos, v), dptr(talos, adv), talos.ptr(q), B, A)
+        ctx.synchronize()
+        q_ref = om.dueling_combine(v, adv)
+        assert max_err(q, q_ref) <= 1e-6
+        g = orc.f32r(orc.rng_normal(82, (B, A))); dv0 = orc.f32r(orc.rng_normal(83, (B, 1))); da0 = orc.f32r(orc.rng_normal(84, (B, A)))
+        dv_ref, da_ref = om.dueling_combine_bwd(g)
+        for acc in (0, 1):
+            dv = dev(dv0); da = dev(da0)
+            talos.lib.talos_dueling_combine_bwd(ctx.handle, dptr(talos, g), talos.ptr(dv), talos.ptr(da), B, A, acc)
+            ctx.synchronize()
+            assert max_err(dv, dv_ref + acc * dv0) <= 2e-6 and max_err(da, da_ref + acc * da0) <= 2e-6
+        qe = orc.f32r(orc.rng_normal(85, (B, A))); qt = orc.f32r(orc.rng_normal(86, (B, A)))
+        qe[0, :] = qe[0, 0]                                       # a tie: the first maximum must win
+        r = orc.f32r(orc.rng_normal(87, (B,))); done = (orc.rng_bounded(88, B, 4) == 0).astype(np.float64)
+        tgt = torch.empty(B, device="cuda:0")
+        talos.lib.talos_dqn_target(ctx.handle, dptr(talos, qe), dptr(talos, qt), dptr(talos, r), dptr(talos, done), 0.99, talos.ptr(tgt), B, A)
+        ctx.synchronize()
+        t_ref = om.dqn_target(qe, qt, r, done, np.float64(np.float32(0.99)))
+        assert max_err(tgt, t_ref) <= 1e-6
+        acts = orc.rng_bounded(89, B, A).astype(np.int32); d_acts = torch.from_numpy(acts).cuda()
+        loss = torch.empty(1, device="cuda:0"); dq = torch.full((B, A), 7.0, device="cuda:0")
+        talos.lib.talos_dqn_loss_fwd_bwd(ctx.handle, talos.ptr(q), talos.ptr(d_acts), talos.ptr(tgt), talos.ptr(loss), talos.ptr(dq), B, A)
+        ctx.synchronize()
+        l_ref, dq_ref = om.dqn_loss_fwd_bwd(q_ref, acts, t_ref)
+        assert abs(host(loss)[0] - l_ref) <= 1e-5 * max(1.0, abs(l_ref)) and max_err(dq, dq_ref) <= 1e-6 * max(1.0, np.abs(dq_ref).max())
+    n = 70000; t0 = orc.f32r(orc.rng_normal(90, (n,))); s0 = orc.f32r(orc.rng_normal(91, (n,)))
+    t = dev(t0)
+    talos.lib.talos_soft_update(ctx.handle, talos.ptr(t), dptr(talos, s0), 0.005, n)
+    ctx.synchronize()
+    assert max_err(t, om.soft_update(t0, s0, np.float64(np.float32(0.005)))) <= 1e-6
+
+
 def test_layout_ops(talos, ctx):
     import ctypes as C
     import torch
