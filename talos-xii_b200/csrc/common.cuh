@@ -131,9 +131,23 @@ void talos_gemm_fp32_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t
                             int64_t lda, int64_t strideA, const float* B, int64_t ldb, int64_t strideB, float* C,
                             int64_t ldc, int64_t strideC, int64_t batch, const EpiArgs& epi);
 // Returns false when the shape/alignment is not eligible (caller falls back to the fp32 kernel).
-bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A,
-                          int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, int mode,
-                          const EpiArgs& epi);
+// First stage of the column sums only: dZ = dY * act'(saved) when dact != 0 (dz may alias dy) and the per-slab column
+// sums of dZ left in `partial` ([slabs][n]); returns the slab count, 0 (nothing launched) when the shape is not served.
+int talos_colsum_partials_launch(talos_ctx* ctx, const float* dy, float* dz, const float* saved, int dact, int64_t rows, int64_t n,
+                                 float* partial, int64_t cap);
+// Optional extras for callers that run the same products every step (the PPO trainer):
+//  * b_hi / b_lo: the B operand already prepared by the caller with the same shape and pitch as B -- in 3xTF32 mode its
+//    TF32 hi / lo split, in TF32 mode b_hi = B rounded to TF32 (b_lo unused) -- so the per-call preparation kernel is
+//    skipped (weights change once per optimizer step, not once per product);
+//  * partial / partial_floats / splits_out: when the product is split along K, leave the `*splits_out` partial results
+//    [splits][M][N] in `partial` (dense, pitch N) and do NOT reduce them into C -- the caller reduces several products'
+//    partials in one launch.  *splits_out = 1 means C was written directly (no split, or `partial` too small).
+struct TcExtra {
+  const float* b_hi = nullptr; const float* b_lo = nullptr;
+  float* partial = nullptr; size_t partial_floats = 0; int* splits_out = nullptr;
+};
+bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                          const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcExtra* extra = nullptr);
 // dZ = dY * act'(saved) (dz may alias dy) and db (+)= column sums of dZ in one pass over the rows; false when the
 // shape is not served by the vector kernel (n % 4 != 0, n > 1024 or unaligned), in which case nothing was launched.
 bool talos_dact_colsum_launch(talos_ctx* ctx, const float* dy, float* dz, const float* saved, int dact, float* db, int64_t rows, int64_t n,

@@ -305,14 +305,17 @@ void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, c
   else launch_one<BN, STAGES, X3, true, true, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
 }
 
+static inline bool x3_mode(int mode) { return mode == TALOS_MODE_TF32X3; }
 thread_local bool g_check_pair = false;   // set by the start-up self-check so that its short reduction still exercises the pair kernel
 
 // A batched product: `batch` independent GEMMs whose operands are `stride*` elements apart (batch 1: a plain GEMM).
 struct TcBatch { int64_t batch, stride_a, stride_b, stride_c; };
 
 void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
-               int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcBatch& bt = TcBatch{1, 0, 0, 0}) {
+               int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcBatch& bt = TcBatch{1, 0, 0, 0},
+               const TcExtra* extra = nullptr) {
   const bool batched = bt.batch > 1;
+  const bool b_given = extra && extra->b_hi && !batched && (x3_mode(mode) ? extra->b_lo != nullptr : true);
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
   int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
   // Short reductions over tall outputs are bound by the epilogue, not the main loop: 128-wide tiles with a
@@ -349,16 +352,22 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // kernel-level scratch: [split-K partials][TF32-rounded copy of the small operand]
   const int64_t a_rows = a_mn ? K : M, a_cols = a_mn ? M : K, b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
   const int64_t a_elems = a_rows * a_cols, b_elems = b_rows * b_cols;
-  const bool round_a = !batched && !x3 && a_elems <= b_elems && a_elems <= (1 << 20), round_b = !batched && !x3 && !round_a && b_elems <= (1 << 20);
+  const bool round_a = !batched && !x3 && !b_given && a_elems <= b_elems && a_elems <= (1 << 20);
+  const bool round_b = !batched && !x3 && !b_given && !round_a && b_elems <= (1 << 20);
   const int64_t r_rows = round_a ? a_rows : b_rows, r_cols = round_a ? a_cols : b_cols, r_ld = (r_cols + 3) & ~int64_t(3);
-  const size_t partial_bytes = splits > 1 ? ((sizeof(float) * (size_t)splits * M * N + 255) & ~size_t(255)) : 0;
-  const bool presplit = !batched && x3 && b_elems <= (1 << 20);
+  const bool plain_epi = !epi.bias && !epi.aux_out && !epi.aux_in && !epi.act && !epi.beta;    // the reduction kernel applies the epilogue
+  const bool keep_partials = extra && extra->partial && splits > 1 && plain_epi && extra->partial_floats >= (size_t)splits * M * N;
+  if (extra && extra->splits_out) *extra->splits_out = keep_partials ? splits : 1;
+  const size_t partial_bytes = (splits > 1 && !keep_partials) ? ((sizeof(float) * (size_t)splits * M * N + 255) & ~size_t(255)) : 0;
+  const bool presplit = !batched && x3 && (b_given || b_elems <= (1 << 20));
   const int64_t s_ld = (b_cols + 3) & ~int64_t(3);
-  const size_t round_bytes = (round_a || round_b) ? sizeof(float) * (size_t)(r_rows * r_ld) : presplit ? 2 * sizeof(float) * (size_t)(b_rows * s_ld) : 0;
+  const size_t round_bytes = (round_a || round_b) ? sizeof(float) * (size_t)(r_rows * r_ld) : (presplit && !b_given) ? 2 * sizeof(float) * (size_t)(b_rows * s_ld) : 0;
   char* scratch = (partial_bytes + round_bytes) ? (char*)talos_workspace(ctx, partial_bytes + round_bytes) : nullptr;
-  if (splits > 1) g.partial = (float*)scratch;
+  if (splits > 1) g.partial = keep_partials ? extra->partial : (float*)scratch;
   const float* B_lo = nullptr;
-  if (presplit) {
+  if (b_given) {                       // prepared by the caller: same shape and pitch as B
+    B = extra->b_hi; B_lo = x3 ? extra->b_lo : nullptr;
+  } else if (presplit) {
     float* hi = (float*)(scratch + partial_bytes); float* lo = hi + b_rows * s_ld;
     split_tf32_kernel<<<(unsigned)ceil_div(b_rows * s_ld, 256), 256, 0, ctx->stream>>>(B, ldb, (int)b_rows, (int)b_cols, (int)s_ld, hi, lo);
     talos_launched(ctx, "split_tf32");
@@ -391,7 +400,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   if (pair) {
     talos_gemm_tc2_launch(ctx, a_mn, b_mn, x3, presplit, ta, tb, tc, tbl, g, 2 * std::min(tiles * splits, workers));
-    if (splits > 1) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
+    if (splits > 1 && !keep_partials) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
     return;
   }
   int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count * (skinny ? 2 : 1));
@@ -404,7 +413,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   }
   TALOS_TC_CASE(256, 4, 2) else TALOS_TC_CASE(128, 6, 3) else TALOS_TC_CASE(64, 8, 4) else TALOS_TC_CASE(32, 8, 4)
 #undef TALOS_TC_CASE
-  if (splits > 1) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
+  if (splits > 1 && !keep_partials) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
 }
 
 // Start-up self-check: every operand layout in both modes against the fp32 CUDA-core kernel on a
@@ -486,13 +495,15 @@ static bool tc_ready(talos_ctx* ctx) {
 }
 
 bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
-                          const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi) {
+                          const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcExtra* extra) {
+  if (extra && extra->splits_out) *extra->splits_out = 1;
   if (ctx->tc_state < 0) return false;
   // TMA needs 16-byte aligned bases and row pitches; tiny problems are launch-bound and stay on CUDA cores.
   if ((((uintptr_t)A | (uintptr_t)B) & 15) || (lda & 3) || (ldb & 3) || K < 1) return false;
   if (M * N * K < (1LL << 18) || M < 1 || N < 1) return false;
   if (!tc_ready(ctx)) return false;
-  tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, epi);
+  if (extra && extra->b_hi && ((((uintptr_t)extra->b_hi | (uintptr_t)extra->b_lo) & 15) != 0)) return false;
+  tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, epi, TcBatch{1, 0, 0, 0}, extra);
   return true;
 }
 

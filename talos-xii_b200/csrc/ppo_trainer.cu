@@ -17,6 +17,12 @@ struct talos_ppo {
   float *params, *grads, *m, *v;       // grads has 4 extra floats: {sum loss, sum kl, count, unused}
   float *h1, *h2, *z, *dz, *dh2, *dh1; // activations for one minibatch
   float* step_stats;                   // [max_steps][4] copy of the tail after each step's exchange
+  // Tensor-core modes: the weights prepared once per optimizer step instead of once per product (same layout as
+  // params): w_hi = TF32-rounded weights, w_lo = TF32-rounded remainder (3xTF32 only).
+  float *w_hi = nullptr, *w_lo = nullptr; bool weights_prepared = false;
+  // The split-K partial results of the three weight-gradient products and the row-slab partial sums of the three
+  // bias gradients stay here until ONE kernel reduces all six into the flat gradient buffer.
+  float* partials = nullptr; int64_t cap_w2 = 0, cap_w1 = 0, cap_wh = 0, cap_b = 0;
   int64_t t = 0; int64_t steps_in_epoch = 0; int64_t last_launches = 0;
   std::vector<float> host_tmp;
   cudaStream_t copy_stream = nullptr;  // host->device staging of talos_ppo_update_host, overlapped with the steps
@@ -31,6 +37,69 @@ void gemm(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, con
           int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& e) {
   if (mode != TALOS_MODE_FP32 && talos_gemm_tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, e)) return;
   talos_gemm_fp32_launch(ctx, opA, opB, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, e);
+}
+
+// gemm() with the weight operand B taken from the prepared copies (when the mode uses them).
+void gemm_w(talos_ppo* p, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, int64_t w_off, int64_t ldb,
+            float* C, int64_t ldc, const EpiArgs& e) {
+  talos_ctx* ctx = p->ctx; const int mode = p->cfg.mode; const float* B = p->params + w_off;
+  TcExtra x; if (p->w_hi) { x.b_hi = p->w_hi + w_off; x.b_lo = p->w_lo ? p->w_lo + w_off : nullptr; }
+  if (mode != TALOS_MODE_FP32 && talos_gemm_tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, e, &x)) return;
+  talos_gemm_fp32_launch(ctx, opA, opB, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0, 1, e);
+}
+// Weight-gradient product C = A^T.B that may leave its split-K partials in `partial` (returns their count, or 0 when
+// C was written directly).
+int gemm_dw(talos_ppo* p, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B, int64_t ldb, float* C, float* partial,
+            int64_t cap) {
+  talos_ctx* ctx = p->ctx; const int mode = p->cfg.mode; int splits = 1;
+  EpiArgs none{nullptr, nullptr, 0, nullptr, 0, 0, 0, 0};
+  TcExtra x; x.partial = partial; x.partial_floats = (size_t)cap; x.splits_out = &splits;
+  if (mode != TALOS_MODE_FP32 && talos_gemm_tc_launch(ctx, 1, 0, M, N, K, A, lda, B, ldb, C, N, mode, none, &x)) return splits > 1 ? splits : 0;
+  talos_gemm_fp32_launch(ctx, 1, 0, M, N, K, A, lda, 0, B, ldb, 0, C, N, 0, 1, none);
+  return 0;
+}
+
+__global__ void prepare_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float a = w[i];
+  const float h = __uint_as_float((__float_as_uint(a) + 0x1000u) & 0xFFFFE000u);        // round to nearest TF32, ties away
+  hi[i] = h;
+  if (lo) lo[i] = __uint_as_float((__float_as_uint(a - h) + 0x1000u) & 0xFFFFE000u);
+}
+void ensure_weights_prepared(talos_ppo* p) {
+  if (!p->w_hi || p->weights_prepared) return;
+  prepare_weights_kernel<<<(unsigned)ceil_div(p->n_int, 256), 256, 0, p->ctx->stream>>>(p->params, p->w_hi, p->w_lo, p->n_int);
+  talos_launched(p->ctx, "prepare_weights");
+  p->weights_prepared = true;
+}
+
+// One launch for the whole flat gradient: segment s of `dst` (n elements) = sum over `slabs` partial rows of length n,
+// added in a fixed order (eight slab lanes per column, each striding the slabs, then the eight lane sums in lane
+// order): deterministic and independent of the launch geometry.  Segments with slabs = 0 were written directly.
+struct GradSegs { float* dst[6]; const float* src[6]; int n[6]; int slabs[6]; int first_block[7]; };
+__global__ void __launch_bounds__(256)
+grad_gather_kernel(GradSegs g) {
+  __shared__ float sh[8][33];
+  int s = 0;
+  while (s < 5 && (int)blockIdx.x >= g.first_block[s + 1]) ++s;
+  const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
+  const int c = ((int)blockIdx.x - g.first_block[s]) * 32 + cl;
+  const int n = g.n[s], slabs = g.slabs[s];
+  const float* src = g.src[s];
+  float acc = 0.f;
+  if (c < n) {
+#pragma unroll 8
+    for (int q = pl; q < slabs; q += 8) acc += src[(size_t)q * n + c];
+  }
+  sh[pl][cl] = acc;
+  __syncthreads();
+  if (pl == 0 && c < n) {
+    float t = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) t += sh[l][cl];
+    g.dst[s][c] = t;
+  }
 }
 
 __global__ void unpack_heads_kernel(const float* __restrict__ z, int HP, int A, long long n, float* __restrict__ logits, float* __restrict__ values) {
@@ -50,13 +119,14 @@ __global__ void log_prob_kernel(const float* __restrict__ z, int HP, int A, cons
 }
 
 void forward(talos_ppo* p, const float* obs, int64_t n) {
-  const auto& c = p->cfg; talos_ctx* ctx = p->ctx; const float* P = p->params;
+  const auto& c = p->cfg; const float* P = p->params;
+  ensure_weights_prepared(p);
   EpiArgs e1{P + p->o_b1, nullptr, 0, nullptr, 0, TALOS_ACT_TANH, 0, 0};
-  gemm(ctx, 0, 0, n, c.hidden, c.obs_dim, obs, c.obs_dim, P + p->o_w1, c.hidden, p->h1, c.hidden, c.mode, e1);
+  gemm_w(p, 0, 0, n, c.hidden, c.obs_dim, obs, c.obs_dim, p->o_w1, c.hidden, p->h1, c.hidden, e1);
   EpiArgs e2{P + p->o_b2, nullptr, 0, nullptr, 0, TALOS_ACT_TANH, 0, 0};
-  gemm(ctx, 0, 0, n, c.hidden, c.hidden, p->h1, c.hidden, P + p->o_w2, c.hidden, p->h2, c.hidden, c.mode, e2);
+  gemm_w(p, 0, 0, n, c.hidden, c.hidden, p->h1, c.hidden, p->o_w2, c.hidden, p->h2, c.hidden, e2);
   EpiArgs e3{P + p->o_bh, nullptr, 0, nullptr, 0, 0, 0, 0};
-  gemm(ctx, 0, 0, n, p->HP, c.hidden, p->h2, c.hidden, P + p->o_wh, p->HP, p->z, p->HP, c.mode, e3);
+  gemm_w(p, 0, 0, n, p->HP, c.hidden, p->h2, c.hidden, p->o_wh, p->HP, p->z, p->HP, e3);
 }
 
 void pack_params(talos_ppo* p, const float* canon, float* internal) {
@@ -106,34 +176,57 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
                                            c.c_value, c.c_entropy, 1.0f, p->dz, HP, p->dz + c.n_actions, HP, tail);
   if (st) throw talos_error(st, talos_last_error_string());
   EpiArgs none{nullptr, nullptr, 0, nullptr, 0, 0, 0, 0};
-  // heads: dWh = h2^T.dz ; dbh = colsum(dz) ; dh2 = (dz.Wh^T) * (1 - h2^2)
-  gemm(ctx, 1, 0, H, HP, n, p->h2, H, p->dz, HP, G + p->o_wh, HP, c.mode, none);
-  if ((st = talos_colsum(ctx, p->dz, G + p->o_bh, n, HP, 0))) throw talos_error(st, talos_last_error_string());
+  // Each gradient is either written straight into G or left as partial sums (split-K slabs of a weight-gradient
+  // product, row-slab column sums of a bias gradient) that ONE gather kernel reduces into G at the end, instead of
+  // six small reduction launches.
+  float* part_w2 = p->partials; float* part_w1 = part_w2 + p->cap_w2; float* part_wh = part_w1 + p->cap_w1;
+  float* part_b2 = part_wh + p->cap_wh; float* part_b1 = part_b2 + p->cap_b; float* part_bh = part_b1 + p->cap_b;
+  GradSegs gs{};
+  auto seg = [&](int i, float* dst, const float* src, int64_t count, int slabs) { gs.dst[i] = dst; gs.src[i] = src; gs.n[i] = (int)count; gs.slabs[i] = slabs; };
+  // column sums of `dy` (times tanh'(h_saved) in place when h_saved is given): partial slabs, or directly into db
+  auto bias_grad = [&](int i, float* dy, const float* h_saved, int64_t width, float* db, float* part) {
+    int slabs = p->partials ? talos_colsum_partials_launch(ctx, dy, dy, h_saved, h_saved ? TALOS_ACT_TANH : 0, n, width, part, p->cap_b) : 0;
+    if (slabs == 0) {
+      if (h_saved) { if (!talos_dact_colsum_launch(ctx, dy, dy, h_saved, TALOS_ACT_TANH, db, n, width, 0)) throw talos_error(TALOS_ERR_CUDA, "dact + colsum kernel refused an aligned shape"); }
+      else { talos_status s2 = talos_colsum(ctx, dy, db, n, width, 0); if (s2) throw talos_error(s2, talos_last_error_string()); }
+    }
+    seg(i, db, part, width, slabs);
+  };
   // dH = (dZ_next . W^T) * tanh'(h), db = colsum(dH).  The tanh' factor is not fused into the GEMM's epilogue when
   // the streaming kernel can take it: that epilogue reads the saved activation row by row and is what bounds these
   // skinny GEMMs (72 -> ~30 us at K = 32); one streaming pass applies the factor in place and produces the bias
   // gradient's column sums at the same time.
-  auto backprop_hidden = [&](const float* dz_next, int64_t k, const float* W, float* dh, const float* h_saved, float* db) {
+  auto backprop_hidden = [&](int i, const float* dz_next, int64_t k, int64_t w_off, float* dh, const float* h_saved, float* db, float* part) {
     if (H % 4 == 0 && H <= 1024) {                                              // what the streaming kernel takes (buffers are aligned)
-      gemm(ctx, 0, 1, n, H, k, dz_next, k, W, k, dh, H, c.mode, none);
-      if (!talos_dact_colsum_launch(ctx, dh, dh, h_saved, TALOS_ACT_TANH, db, n, H, 0)) throw talos_error(TALOS_ERR_CUDA, "dact + colsum kernel refused an aligned shape");
+      gemm_w(p, 0, 1, n, H, k, dz_next, k, w_off, k, dh, H, none);
+      bias_grad(i, dh, h_saved, H, db, part);
       return;
     }
     EpiArgs d{nullptr, nullptr, 0, h_saved, H, 0, TALOS_ACT_TANH, 0};
-    gemm(ctx, 0, 1, n, H, k, dz_next, k, W, k, dh, H, c.mode, d);
-    talos_status s2 = talos_colsum(ctx, dh, db, n, H, 0);
-    if (s2) throw talos_error(s2, talos_last_error_string());
+    gemm_w(p, 0, 1, n, H, k, dz_next, k, w_off, k, dh, H, d);
+    bias_grad(i, dh, nullptr, H, db, part);
   };
-  backprop_hidden(p->dz, HP, P + p->o_wh, p->dh2, p->h2, G + p->o_b2);
+  // heads: dWh = h2^T.dz ; dbh = colsum(dz) ; dh2 = (dz.Wh^T) * (1 - h2^2)
+  seg(0, G + p->o_wh, part_wh, H * HP, gemm_dw(p, H, HP, n, p->h2, H, p->dz, HP, G + p->o_wh, p->partials ? part_wh : nullptr, p->cap_wh));
+  bias_grad(1, p->dz, nullptr, HP, G + p->o_bh, part_bh);
+  backprop_hidden(2, p->dz, HP, p->o_wh, p->dh2, p->h2, G + p->o_b2, part_b2);
   // layer 2
-  gemm(ctx, 1, 0, H, H, n, p->h1, H, p->dh2, H, G + p->o_w2, H, c.mode, none);
-  backprop_hidden(p->dh2, H, P + p->o_w2, p->dh1, p->h1, G + p->o_b1);
+  seg(3, G + p->o_w2, part_w2, H * H, gemm_dw(p, H, H, n, p->h1, H, p->dh2, H, G + p->o_w2, p->partials ? part_w2 : nullptr, p->cap_w2));
+  backprop_hidden(4, p->dh2, H, p->o_w2, p->dh1, p->h1, G + p->o_b1, part_b1);
   // layer 1 (no gradient w.r.t. the observations)
-  gemm(ctx, 1, 0, c.obs_dim, H, n, obs, c.obs_dim, p->dh1, H, G + p->o_w1, H, c.mode, none);
+  seg(5, G + p->o_w1, part_w1, c.obs_dim * H, gemm_dw(p, c.obs_dim, H, n, obs, c.obs_dim, p->dh1, H, G + p->o_w1, p->partials ? part_w1 : nullptr, p->cap_w1));
+  {
+    int blocks = 0;
+    for (int i = 0; i < 6; ++i) { gs.first_block[i] = blocks; if (gs.slabs[i] > 0) blocks += (int)ceil_div(gs.n[i], 32); }
+    gs.first_block[6] = blocks;
+    if (blocks > 0) { grad_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(gs); talos_launched(ctx, "grad_gather"); }
+  }
   if (comm) { if ((st = talos_comm_allreduce_sum(comm, G, p->n_int + 4))) throw talos_error(st, talos_last_error_string()); }
   p->t += 1;
   float* stat_slot = p->step_stats + 4 * (p->steps_in_epoch % MAX_STEPS_PER_EPOCH);
   talos_adam_launch(ctx, p->params, G, p->m, p->v, p->n_int, p->t, c.lr, c.beta1, c.beta2, c.eps, 1.0f, tail + 2, 0.f, stat_slot);
+  p->weights_prepared = false;
+  ensure_weights_prepared(p);                                  // for the next step's products (and the caller's next forward)
   p->steps_in_epoch += 1;
   p->last_launches = ctx->launches.load() - l0;
 }
@@ -195,6 +288,16 @@ TALOS_API talos_status talos_ppo_create(talos_ctx* ctx, const talos_ppo_config* 
   alloc(&p->h1, mb * H); alloc(&p->h2, mb * H); alloc(&p->dh1, mb * H); alloc(&p->dh2, mb * H);
   alloc(&p->z, mb * p->HP); alloc(&p->dz, mb * p->HP);
   alloc(&p->step_stats, 4 * MAX_STEPS_PER_EPOCH);
+  if (cfg->mode != TALOS_MODE_FP32) {
+    alloc(&p->w_hi, p->n_int);
+    if (cfg->mode == TALOS_MODE_TF32X3) alloc(&p->w_lo, p->n_int);
+    // room for the largest split count the GEMM launcher picks: one slab per 512 reduction elements in 3xTF32 mode
+    // (never more than that), at most one per SM otherwise
+    const int64_t max_splits = std::max<int64_t>(ctx->sm_count, mb / 512 + 1) + 1;
+    p->cap_w2 = up4(max_splits * H * H); p->cap_w1 = up4(max_splits * O * H); p->cap_wh = up4(max_splits * H * p->HP);
+    p->cap_b = up4((4 * (int64_t)ctx->sm_count + 1) * std::max<int64_t>(H, p->HP));
+    alloc(&p->partials, p->cap_w2 + p->cap_w1 + p->cap_wh + 3 * p->cap_b);
+  }
   *out = p;
   TALOS_ENTRY_END
 }
@@ -203,7 +306,7 @@ TALOS_API talos_status talos_ppo_destroy(talos_ppo* p) {
   TALOS_ENTRY_BEGIN
   if (!p) return TALOS_OK;
   cudaSetDevice(p->ctx->device); cudaStreamSynchronize(p->ctx->stream);
-  for (float* q : {p->params, p->grads, p->m, p->v, p->h1, p->h2, p->dh1, p->dh2, p->z, p->dz, p->step_stats}) cudaFree(q);
+  for (float* q : {p->params, p->grads, p->m, p->v, p->h1, p->h2, p->dh1, p->dh2, p->z, p->dz, p->step_stats, p->w_hi, p->w_lo, p->partials}) cudaFree(q);
   for (cudaEvent_t ev : p->chunk_ready) cudaEventDestroy(ev);
   if (p->staging_free) cudaEventDestroy(p->staging_free);
   if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
@@ -227,6 +330,7 @@ TALOS_API talos_status talos_ppo_set_params_host(talos_ppo* p, const float* flat
   pack_params(p, flat, p->host_tmp.data());
   TALOS_CHECK_CUDA(cudaMemcpyAsync(p->params, p->host_tmp.data(), sizeof(float) * (size_t)p->n_int, cudaMemcpyHostToDevice, p->ctx->stream));
   TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  p->weights_prepared = false;
   TALOS_ENTRY_END
 }
 TALOS_API talos_status talos_ppo_get_params_host(talos_ppo* p, float* flat) {

@@ -441,13 +441,17 @@ TALOS_API talos_status talos_rmsnorm_bwd(talos_ctx* ctx, const float* dy, const 
 
 // out[c] (+)= sum_r g[r][c]; with dact != 0 the summand is g_out[r][c] = g[r][c] * act'(saved[r][c]), also written
 // (vector path only: n % 4 == 0, n <= 1024, 16-byte aligned; returns false when the shape needs the plain path).
-static bool colsum_vec_launch(talos_ctx* ctx, const float* g, float* g_out, const float* saved, int dact, float* out, int64_t rows, int64_t n, int accumulate) {
+// `ext_partial` / `ext_cap` / `slabs_out`: leave the per-slab partial sums [slabs][n] in the caller's buffer and skip
+// the second stage (the caller reduces them later); `out` is then unused.
+static bool colsum_vec_launch(talos_ctx* ctx, const float* g, float* g_out, const float* saved, int dact, float* out, int64_t rows, int64_t n, int accumulate,
+                              float* ext_partial = nullptr, int64_t ext_cap = 0, int* slabs_out = nullptr) {
   const bool vec = (n % 4 == 0) && n <= 1024 && aligned16(g) && (!dact || (aligned16(saved) && aligned16(g_out)));
   if (!vec) return false;
   const int n4 = (int)(n / 4);
   int64_t slabs = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 32), 4 * (int64_t)ctx->sm_count));
   int64_t rows_per = std::max<int64_t>(1, ceil_div(rows, slabs)); slabs = std::max<int64_t>(1, ceil_div(rows, rows_per));
-  float* partial = (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
+  if (ext_partial && (ext_cap < slabs * n || !aligned16(ext_partial))) return false;
+  float* partial = ext_partial ? ext_partial : (float*)talos_workspace(ctx, sizeof(float) * (size_t)slabs * n);
   size_t shmem = sizeof(float4) * (size_t)(256 / n4) * n4;
   auto G4 = (const float4*)g; auto O4 = (float4*)g_out; auto S4 = (const float4*)saved;
   switch (dact) {
@@ -458,9 +462,18 @@ static bool colsum_vec_launch(talos_ctx* ctx, const float* g, float* g_out, cons
     default: throw talos_error(TALOS_ERR_ARG, "bad activation kind");
   }
   talos_launched(ctx, "colsum_stage1");
+  if (ext_partial) { *slabs_out = (int)slabs; return true; }
   colsum_partials_kernel<<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(partial, (int)slabs, (int)n, out, accumulate ? 1 : 0);
   talos_launched(ctx, "colsum_stage2");
   return true;
+}
+
+// Internal (PPO trainer): the first stage only -- dZ = dY * act'(saved) when dact != 0 (dz may alias dy), per-slab
+// column sums of dZ left in `partial` ([slabs][n]).  Returns the slab count, 0 when the shape is not served.
+int talos_colsum_partials_launch(talos_ctx* ctx, const float* dy, float* dz, const float* saved, int dact, int64_t rows, int64_t n,
+                                 float* partial, int64_t cap) {
+  int slabs = 0;
+  return colsum_vec_launch(ctx, dy, dz, saved, dact, nullptr, rows, n, 0, partial, cap, &slabs) ? slabs : 0;
 }
 
 // Internal (Linear backward, PPO trainer): dZ = dY * act'(saved) (dz may be dy), db (+)= colsum(dZ) in one pass.
