@@ -86,11 +86,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (lane == 0) {
       prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); if (BPS) prefetch_tmap(&tmap_b_lo);
       int stage = 0; uint32_t phase = 0; bool ok = true;
+      // L2 prefetch of the streamed operands, PF_DIST k-blocks ahead of the loads along this CTA's own (item, k-block)
+      // sequence: with two or three stages in flight the pipeline cannot cover DRAM latency by itself, but it does
+      // cover the latency of an L2 hit.
+      constexpr int PF_DIST = STAGES + 4;
+      int pf_it = blockIdx.x, pf_kb = 0, pf_kb1 = 0, pf_mb = 0, pf_nb = 0, pf_bz = 0;
+      auto pf_decode = [&]() {
+        if (pf_it >= items) return;
+        pf_bz = pf_it / per_batch; const int r = pf_it - pf_bz * per_batch;
+        const int ks = r / tiles_mn, rem = r % tiles_mn; pf_nb = rem / g.m_tiles; pf_mb = rem % g.m_tiles;
+        pf_kb = ks * g.kb_per_split; pf_kb1 = min(g.kb_total, pf_kb + g.kb_per_split);
+      };
+      auto pf_step = [&]() {                                   // prefetch the k-block at the look-ahead position, then advance it
+        if (pf_it >= items) return;
+        if (g.pf_a) {
+          if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_prefetch_3d(&tmap_a, pf_mb * BM + 32 * j, pf_kb * BK, pf_bz); }
+          else tma_prefetch_3d(&tmap_a, pf_kb * BK, pf_mb * BM, pf_bz);
+        }
+        if (g.pf_b) {
+          if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_prefetch_3d(&tmap_b, pf_nb * BN + 32 * j, pf_kb * BK, pf_bz); }
+          else tma_prefetch_3d(&tmap_b, pf_kb * BK, pf_nb * BN, pf_bz);
+        }
+        if (++pf_kb >= pf_kb1) { pf_it += gridDim.x; pf_decode(); }
+      };
+      const bool pf_on = g.pf_a || g.pf_b;
+      if (pf_on) { pf_decode(); for (int i = 0; i < PF_DIST; ++i) pf_step(); }
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
         const int bz = it / per_batch, r = it - bz * per_batch;
         const int ks = r / tiles_mn, rem = r % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
+          if (pf_on) pf_step();
           if (!mbar_wait(empty + stage, phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(full + stage, A_BYTES + B_BYTES + (BPS ? B_BYTES : 0));
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
@@ -326,6 +352,15 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
+  // Streamed K-major operands (more than 8 MB, i.e. not something that stays in L2 anyway) of the 3xTF32 kernels are
+  // prefetched into L2 ahead of the loads: those kernels have only two or three stages in flight.  Measured on
+  // 65 536 x 256 x 256: 3xTF32 A.B 65.0 -> 59.7 us, A.B^T 63.4 -> 59.3 us; the TF32 kernels (four or more stages)
+  // and MN-major operands (one prefetch per 32-column box) got slower with it, so they do not use it.
+  {
+    const bool pf_off = getenv("TALOS_TC_NO_PREFETCH") != nullptr;
+    g.pf_a = (!pf_off && x3 && !a_mn && (int64_t)M * K * g.batch > (2 << 20)) ? 1 : 0;
+    g.pf_b = (!pf_off && x3 && !b_mn && (int64_t)N * K * g.batch > (2 << 20)) ? 1 : 0;
+  }
   // 256-wide outputs with at least 256 rows and a long reduction run on CTA pairs (cta_group::2): 256 x 256 tiles
   // halve the operand bytes each SM has to pull per flop.  For short reductions (K = 256: 8 k-blocks a tile) the
   // pair's start-up and cross-CTA hand-offs cost more than that saves (measured 8 % slower at K = 256, 10 % faster

@@ -14,6 +14,7 @@ struct TcArgs {
   EpiArgs epi;
   int32_t* status;
   int tma_out;                             // 1: results leave through TMA stores (tmap_c), 0: direct stores
+  int pf_a, pf_b;                          // prefetch this operand's tiles into L2 a few k-blocks ahead (large streamed operands only)
   int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
   long long stride_c;                      // elements between consecutive batch members of C
 };
@@ -66,6 +67,10 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Ask the copy engine to bring one box of a tensor map into L2 (no shared-memory destination, no completion signal).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
