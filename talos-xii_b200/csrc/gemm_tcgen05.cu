@@ -372,16 +372,29 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   g.m_tiles = (int)ceil_div(M, pair ? 2 * BM : BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
   int tiles = g.m_tiles * g.n_tiles, splits = 1;
   const int workers = pair ? ctx->sm_count / 2 : ctx->sm_count;   // CTAs, or CTA pairs
-  if (!batched && tiles * 2 <= workers && g.kb_total >= 16) {
-    splits = (int)std::min<int64_t>(workers / tiles, g.kb_total / 8);
-    if (splits < 2) splits = 1;
+  // Split K when the output tiles alone cannot occupy the workers.  The tensor core truncates when it adds into the
+  // fp32 accumulator, a bias that grows with the length of the accumulation chain (measured ~7e-9 relative per k
+  // element), so the fp32-faithful mode never chains more than 512 k elements in TMEM: longer reductions MUST be split
+  // there, and the partial sums are added in fp32 (round-to-nearest) by the reduction kernel.
+  // The split count is chosen per number of rounds r (every worker runs r items): splits = r * workers / tiles, and
+  // the cheapest r * (k-blocks per item + a few k-blocks' worth of per-item pipeline fill and epilogue) wins -- e.g. the
+  // 256 x 256 x 65 536 weight gradient runs 2 x 147 items of 14 k-blocks on 148 CTAs instead of 2 x 128 of 16.
+  const int cap = (x3 && !batched) ? 512 / BK : g.kb_total;     // (batched products with K > 512 are not routed here)
+  g.kb_per_split = g.kb_total;
+  if (!batched && ((tiles * 2 <= workers && g.kb_total >= 16) || g.kb_total > cap)) {
+    const int item_overhead = 3;
+    long long best_cost = -1;
+    for (int r = 1; r <= 8; ++r) {
+      const int s_r = (int)std::max<int64_t>(1, (int64_t)r * workers / tiles);
+      int kps = (int)ceil_div(g.kb_total, s_r);
+      if (kps < 8 && r > 1) break;                                  // items would become shorter than their own overhead
+      kps = std::max(kps, std::min(8, g.kb_total));
+      if (kps > cap) continue;
+      const long long cost = (long long)ceil_div((int64_t)tiles * ceil_div(g.kb_total, kps), workers) * (kps + item_overhead);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; g.kb_per_split = kps; }
+    }
+    if (g.kb_per_split > cap) g.kb_per_split = cap;
   }
-  g.kb_per_split = (int)ceil_div(g.kb_total, splits);
-  // The tensor core truncates when it adds into the fp32 accumulator, a bias that grows with the
-  // length of the accumulation chain (measured ~7e-9 relative per k element).  The fp32-faithful
-  // mode therefore never chains more than 512 k elements in TMEM; longer reductions are split and
-  // the partial sums are added in fp32 (round-to-nearest) by the reduction kernel.
-  if (x3 && !batched && g.kb_per_split > 512 / BK) g.kb_per_split = 512 / BK;   // (batched products with K > 512 are not routed here)
   splits = (int)ceil_div(g.kb_total, g.kb_per_split);
   g.splits = splits;
   // kernel-level scratch: [split-K partials][TF32-rounded copy of the small operand]

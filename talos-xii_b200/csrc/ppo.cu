@@ -15,7 +15,7 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
                 const int* __restrict__ actions, const float* __restrict__ old_logp, const float* __restrict__ adv,
                 const float* __restrict__ ret, long long n, int n_actions, float clip, float c_v, float c_h, float inv_denom,
                 float* __restrict__ dlogits, long long ld_out, float* __restrict__ dvalues, long long dvs,
-                float* __restrict__ partial) {
+                float* __restrict__ partial, int vec) {
   __shared__ float sh_loss[128], sh_kl[128];
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   float loss = 0.f, kl = 0.f;
@@ -23,8 +23,20 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
     const int na = A > 0 ? A : n_actions;
     float l[A > 0 ? A : MAX_ACTIONS];
     float mx = -INFINITY;
+    // each thread owns one row: 128-bit accesses when the row is a whole number of aligned float4 (the host checks)
+    constexpr bool VEC = (A > 0) && (A % 4 == 0);
+    if (VEC && vec) {
 #pragma unroll
-    for (int a = 0; a < na; ++a) { l[a] = logits[i * ld + a]; mx = fmaxf(mx, l[a]); }
+      for (int a = 0; a < na; a += 4) {
+        const float4 q = *(const float4*)(logits + i * ld + a);
+        l[a] = q.x; l[a + 1] = q.y; l[a + 2] = q.z; l[a + 3] = q.w;
+      }
+#pragma unroll
+      for (int a = 0; a < na; ++a) mx = fmaxf(mx, l[a]);
+    } else {
+#pragma unroll
+      for (int a = 0; a < na; ++a) { l[a] = logits[i * ld + a]; mx = fmaxf(mx, l[a]); }
+    }
     float se = 0.f;
 #pragma unroll
     for (int a = 0; a < na; ++a) se += expf(l[a] - mx);
@@ -56,8 +68,20 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
       float d = c_h * p * (lp + 1.f) + (a == act ? d_lp_a : 0.f);
       sum_d += d; l[a] = d;
     }
+    // p_j again from logp_j = log p_j: kept as p in a second pass to spare registers
+    if (VEC && vec) {
 #pragma unroll
-    for (int a = 0; a < na; ++a) { float lp_p = expf(logits[i * ld + a] - lse); dlogits[i * ld_out + a] = (l[a] - lp_p * sum_d) * inv_denom; }
+      for (int a = 0; a < na; a += 4) {
+        const float4 q = *(const float4*)(logits + i * ld + a);
+        float4 o;
+        o.x = (l[a] - expf(q.x - lse) * sum_d) * inv_denom; o.y = (l[a + 1] - expf(q.y - lse) * sum_d) * inv_denom;
+        o.z = (l[a + 2] - expf(q.z - lse) * sum_d) * inv_denom; o.w = (l[a + 3] - expf(q.w - lse) * sum_d) * inv_denom;
+        *(float4*)(dlogits + i * ld_out + a) = o;
+      }
+    } else {
+#pragma unroll
+      for (int a = 0; a < na; ++a) { float lp_p = expf(logits[i * ld + a] - lse); dlogits[i * ld_out + a] = (l[a] - lp_p * sum_d) * inv_denom; }
+    }
     dvalues[i * dvs] = c_v * 2.f * dvl * inv_denom;
   }
   sh_loss[threadIdx.x] = loss; sh_kl[threadIdx.x] = kl; __syncthreads();
@@ -128,7 +152,8 @@ TALOS_API talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logit
   TALOS_REQUIRE(logits && values && actions && old_logp && adv && ret && dlogits && dvalues && stats, TALOS_ERR_ARG, "null pointer");
   int blocks = (int)ceil_div(n, 128);
   float* partial = (float*)talos_workspace(ctx, sizeof(float) * 2 * (size_t)blocks);
-#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial)
+#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial, vec)
+  const int vec = (((uintptr_t)logits | (uintptr_t)dlogits) & 15) == 0 && ld_logits % 4 == 0 && ld_out % 4 == 0;
   if (n_actions == 16) TALOS_PPO_LAUNCH(16); else if (n_actions == 5) TALOS_PPO_LAUNCH(5); else TALOS_PPO_LAUNCH(0);
 #undef TALOS_PPO_LAUNCH
   talos_launched(ctx, "ppo_loss");
