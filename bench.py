@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: the data-parallel PPO actor-critic update of BASELINE config 5.
+"""Benchmark of the hot path: the data-parallel PPO actor-critic update of benchmark configuration 5.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode tf32x3|tf32|fp32]
 

@@ -59,7 +59,7 @@ def linear_bwd(x, W, g, has_bias, threads=None, need_dx=True):
     db = bias_bwd(g2, W.shape[1]) if has_bias else None
     return (dx.reshape(x.shape) if need_dx else None), dW, db
 
-# ------------------------------------------------------------------ MLP (BASELINE config 2; DQN-style placement, src/dqn.rs:70-74)
+# ------------------------------------------------------------------ MLP (benchmark configuration 2; DQN-style placement, src/dqn.rs:70-74)
 
 
 def mlp_fwd(X, Ws, bs, acts, threads=None):
@@ -365,7 +365,7 @@ def soft_update(target, source, tau):
     """src/dqn.rs:129-150."""
     return target * (1.0 - tau) + source * tau
 
-# ------------------------------------------------------------------ plain multi-head block (BASELINE config 3) -- extension
+# ------------------------------------------------------------------ plain multi-head block (benchmark configuration 3) -- extension
 
 
 def block_fwd(x, P, heads, eps=1e-6, threads=None):
@@ -472,7 +472,7 @@ def adam_step(params, grads, m, v, t, lr, b1=0.9, b2=0.999, eps=1e-8, clip_norm=
 
 
 class MlpActorCritic:
-    """BASELINE config 5 policy (extension): trunk obs->h->h with tanh, policy head h->A, value
+    """benchmark configuration 5 policy (extension): trunk obs->h->h with tanh, policy head h->A, value
     head h->1, the ActorCritic split of src/ppo.rs:247-307 on an MLP trunk."""
     NAMES = ["w1", "b1", "w2", "b2", "wp", "bp", "wv", "bv"]
 

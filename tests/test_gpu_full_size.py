@@ -1,4 +1,4 @@
-"""Full-size checks at the BASELINE configurations' own sizes, where the f64 oracle would take minutes to hours:
+"""Full-size checks at the benchmark configurations' own sizes, where the f64 oracle would take minutes to hours:
 size-independent properties and agreement between independent device implementations (the fp32 CUDA-core kernels
 share no code with the tensor-core kernels)."""
 import ctypes
@@ -46,7 +46,7 @@ def test_gemm_4096_tensor_core_modes_against_the_fp32_kernel_and_linearity(talos
 
 
 def test_config5_full_update_modes_agree_and_minibatch_order_is_the_only_coupling(talos, ctx):
-    # BASELINE config 5 at full length: 1 048 576 transitions, minibatch 65 536, 4 epochs = 64 optimizer steps.
+    # benchmark configuration 5 at full length: 1 048 576 transitions, minibatch 65 536, 4 epochs = 64 optimizer steps.
     import torch
     N, OBS, HID, ACT, MB = 1048576, 64, 256, 16, 65536
     g = torch.Generator(device="cuda:0"); g.manual_seed(30)

@@ -94,7 +94,7 @@ def nrm(seed, shape, std=1.0):
 
 @pytest.mark.parametrize("mode,tol", [(1, 1e-5), (2, 2e-3)])
 def test_config3_transformer_block_forward_backward(mode, tol):
-    # BASELINE config 3 shapes (S64 d256 H8 dh32 ff1024, eps 1e-6, RoPE base 10000 token positions, causal, SiLU);
+    # benchmark configuration 3 shapes (S64 d256 H8 dh32 ff1024, eps 1e-6, RoPE base 10000 token positions, causal, SiLU);
     # the oracle runs a 32-sample batch, the GPU also the full 1024-sample batch.
     Bs, S, D, H = 32, 64, 256, 8
     P = dict(g1=np.ones(D), g2=np.ones(D), w_qkv=nrm(11, (D, 3 * D), 0.02), w_o=nrm(12, (D, D), 0.02), w_ff1=nrm(13, (D, 1024), 0.02),
@@ -120,7 +120,7 @@ def test_config3_transformer_block_forward_backward(mode, tol):
 
 @pytest.mark.parametrize("mode,tol", [(1, 1e-5), (2, 2e-3)])
 def test_config4_mla_forward_both_position_modes(mode, tol):
-    # BASELINE config 4 shapes: S128 d512 latent 64, 8 heads of 64 + rope 32, N(0,0.02^2) weights, non-causal
+    # benchmark configuration 4 shapes: S128 d512 latent 64, 8 heads of 64 + rope 32, N(0,0.02^2) weights, non-causal
     Bs, S, D = 16, 128, 512
     cfg = om.MLAConfig(D, 8, 64, 32, 64, 128)
     shapes = dict(dkv=(D, 64), uk=(64, 512), uv=(64, 512), q=(D, 512), kr=(D, 256), qr=(D, 256), o=(512, D))

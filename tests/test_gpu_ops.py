@@ -55,7 +55,7 @@ def ref_gemm(opA, opB, A, B):
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
 def test_config1_gemm_512_all_forms(talos, ctx, mode):
-    # BASELINE config 1: 512^3, uniform[-1,1) seeds 42/123, A.B, A.B^T, A^T.B
+    # benchmark configuration 1: 512^3, uniform[-1,1) seeds 42/123, A.B, A.B^T, A^T.B
     A = uniform(42, (512, 512)); B = uniform(123, (512, 512))
     for opA, opB in [(0, 0), (0, 1), (1, 0)]:
         got = gemm(talos, ctx, opA, opB, A, B, mode)
@@ -167,7 +167,7 @@ def test_gemm_batched_qkt_and_pv(talos, ctx):
 @pytest.mark.parametrize("mode", [0, 1, 2])
 def test_config2_mlp_forward_backward(talos, ctx, mode):
     import torch
-    # BASELINE config 2: batch 8192, 64 -> 256 -> 256 -> 16, tanh, Xavier-uniform, N(0,1) inputs and upstream grad
+    # benchmark configuration 2: batch 8192, 64 -> 256 -> 256 -> 16, tanh, Xavier-uniform, N(0,1) inputs and upstream grad
     n = 8192; dims = [64, 256, 256, 16]; acts = ["tanh", "tanh", "none"]
     X = normal(1, (n, 64)); dY = normal(5, (n, 16))
     Ws = [xavier(2 + i, dims[i], dims[i + 1]) for i in range(3)]

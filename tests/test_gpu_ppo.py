@@ -56,7 +56,7 @@ def run_case(talos, ctx, N, obs_dim, hidden, A, mb, epochs, mode, lr=3e-4, kl_st
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
 def test_ppo_update_matches_oracle_config5_shape(talos, ctx, mode):
-    # BASELINE config 5 at reduced length: obs 64, trunk 64->256->256 tanh, 16 actions, 4 epochs of consecutive minibatches
+    # benchmark configuration 5 at reduced length: obs 64, trunk 64->256->256 tanh, 16 actions, 4 epochs of consecutive minibatches
     N, mb, epochs = 16384, 4096, 4
     got, ref, kls, ref_kls, init, loss = run_case(talos, ctx, N, 64, 256, 16, mb, epochs, mode)
     tol = TOL[mode]
