@@ -198,14 +198,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll 8
         for (int ci = 0; ci < CONV_ITERS; ++ci) {
           const int i = ct + ci * 128;
-          float4* hi = i < A_BYTES / 16 ? ahi + i : bhi + (i - A_BYTES / 16);
+          const float4* hi = i < A_BYTES / 16 ? ahi + i : bhi + (i - A_BYTES / 16);
           float4* lo = i < A_BYTES / 16 ? alo + i : blo + (i - A_BYTES / 16);
-          float4 v = *hi, h, l;
-          h.x = __uint_as_float(cvt_tf32(v.x)); h.y = __uint_as_float(cvt_tf32(v.y));
-          h.z = __uint_as_float(cvt_tf32(v.z)); h.w = __uint_as_float(cvt_tf32(v.w));
-          l.x = __uint_as_float(cvt_tf32(v.x - h.x)); l.y = __uint_as_float(cvt_tf32(v.y - h.y));
-          l.z = __uint_as_float(cvt_tf32(v.z - h.z)); l.w = __uint_as_float(cvt_tf32(v.w - h.w));
-          *hi = h; *lo = l;
+          *lo = tf32_remainder(*hi);                       // the staged tile itself is the hi operand
         }
         fence_proxy_async();
         __syncwarp();

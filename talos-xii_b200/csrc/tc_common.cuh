@@ -119,6 +119,19 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // bottleneck.  A carry out of the mantissa correctly bumps the exponent; Inf/NaN inputs are not expected here.
 __device__ __forceinline__ uint32_t cvt_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u; }
 
+// 3xTF32 split of four staged fp32 values.  The tensor core reads an fp32 word as TF32 by dropping its low 13 bits
+// (measured: the error of a plain TF32 product matches truncation, and the split below reproduces the fp32 product to
+// 1.8e-6), so the staged tile already IS the hi operand and nothing is written back for it; lo is the remainder
+// against that truncation, rounded to TF32.  hi + lo reproduces the value to 2^-21 relative.
+__device__ __forceinline__ float4 tf32_remainder(float4 v) {
+  float4 l;
+  l.x = __uint_as_float(cvt_tf32(v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u)));
+  l.y = __uint_as_float(cvt_tf32(v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u)));
+  l.z = __uint_as_float(cvt_tf32(v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u)));
+  l.w = __uint_as_float(cvt_tf32(v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u)));
+  return l;
+}
+
 // Shared-memory matrix descriptor for a swizzled operand tile (1024-byte aligned).
 //  K-major : layout 2 (128B swizzle, 16-byte atoms): rows of 128 B, 8-row groups 1024 B apart (SBO);
 //            the leading offset is unused (1).
