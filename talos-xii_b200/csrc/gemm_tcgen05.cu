@@ -339,11 +339,6 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   const bool b_given = extra && extra->b_hi && !batched && (x3_mode(mode) ? extra->b_lo != nullptr : true);
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
   int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
-  // Short reductions over tall outputs are bound by the epilogue, not the main loop: 128-wide tiles with a
-  // two-stage pipeline fit two CTAs per SM (2 x 97 KB shared memory, 2 x 256 TMEM columns), which doubles
-  // the epilogue warps per SM.
-  const bool skinny = !batched && !x3 && N > 64 && K <= 512 && M >= 128LL * 2 * ctx->sm_count && getenv("TALOS_TC_SKINNY") != nullptr;
-  if (skinny) bn = 128;   // (takes precedence over the CTA-pair kernel, which needs bn == 256)
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
@@ -446,8 +441,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
     if (splits > 1 && !keep_partials) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
     return;
   }
-  int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count * (skinny ? 2 : 1));
-  if (skinny) { launch_major<128, 2, false, 2>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid); return; }
+  int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count);
 #define TALOS_TC_CASE(BNv, ST, ST3)                                                                          \
   if (bn == BNv) {                                                                                           \
     if (x3 && presplit) launch_major<BNv, ST3, true, 1, true>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);    \
