@@ -81,6 +81,16 @@ def test_ppo_small_reference_sized_policy(talos, ctx):
     assert np.allclose(kls, ref_kls, rtol=1e-3, atol=1e-8)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+def test_ppo_widths_that_leave_the_fast_paths(talos, ctx, mode):
+    # hidden width 30 (not a multiple of 4: no TMA pitch, no vector column sums, tanh' through the GEMM epilogue),
+    # 7 observations, 3 actions, ragged last minibatch: every fallback of the trainer in one update
+    got, ref, kls, ref_kls, _, _ = run_case(talos, ctx, 700, 7, 30, 3, 256, 2, mode, lr=1e-3)
+    for k in ref:
+        assert rel_err(got[k], ref[k]) <= 2e-5, k
+    assert np.allclose(kls, ref_kls, rtol=1e-3, atol=1e-8)
+
+
 def test_ppo_update_from_host_buffers_and_kl_early_stop(talos, ctx):
     got, ref, kls, ref_kls, _, _ = run_case(talos, ctx, 4096, 64, 256, 16, 1024, 6, 1, lr=3e-2, kl_stop=0.015, via_host=True)
     assert len(kls) == len(ref_kls) and len(kls) < 6          # stops once mean approx-KL > 0.0225 (src/ppo.rs:762-767)
