@@ -270,6 +270,9 @@ def run_ours(args):
     ms, launches = timed(tr, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
     value = args.steps * mb * world / (ms * 1e-3)
+    if args.mode != "fp32" and not ctx.tensor_cores_active:
+        raise SystemExit("bench.py: the tensor-core path is disabled on this context (its start-up self-check failed; run with "
+                         "TALOS_DEBUG=1 to see which case): refusing to report the fp32 fallback as a %s figure" % args.mode)
 
     # ---- end to end through the host-buffer entry point: H2D of every step's transitions inside the timed region
     e2e_steps = min(args.steps, n_mb)

@@ -385,6 +385,21 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
     }
     if (g.kb_per_split > cap) g.kb_per_split = cap;
   }
+  g.chain_kb = 0;
+  if (pair && x3 && g.kb_total > cap && !getenv("TALOS_TC_NO_FOLD")) {
+    // CTA-pair kernel: the chain cap is met ON CHIP (finished chains are folded into a running sum in TMEM), so K is
+    // split through memory only as far as it takes to keep the pairs busy: the smallest power-of-two split whose
+    // last round is at least 95 % full (4096^3: 2 slabs of 4 chains instead of 8 slabs through memory).
+    int best_s = 1; double best_eff = 0.0;
+    for (int s_ext = 1; s_ext <= 8 && g.kb_total / s_ext >= cap; s_ext *= 2) {
+      const int64_t n_items = (int64_t)tiles * s_ext, rounds = ceil_div(n_items, workers);
+      const double eff = (double)n_items / (double)(rounds * workers);
+      if (eff > best_eff + 0.03) { best_eff = eff; best_s = s_ext; }
+      if (eff >= 0.95) break;
+    }
+    g.kb_per_split = (int)(ceil_div(ceil_div(g.kb_total, best_s), cap) * cap);     // whole chains per item
+    g.chain_kb = cap;
+  }
   splits = (int)ceil_div(g.kb_total, g.kb_per_split);
   g.splits = splits;
   // kernel-level scratch: [split-K partials][TF32-rounded copy of the small operand]
@@ -495,7 +510,7 @@ bool self_check_shape(talos_ctx* ctx, const int M, const int N = 328, const int 
             }
           double rel = sqrt(num / (den > 0 ? den : 1));
           if (dbg) fprintf(stderr, "[talos self-check]   rel err %.3e  c[0]=%g ref %g c[last]=%g ref %g\n", rel, r1[0], r0[0], r1[(size_t)(M - 1) * LD + N - 1], r0[(size_t)(M - 1) * LD + N - 1]);
-          bool good = rel <= (mode == TALOS_MODE_TF32 ? 2e-3 : 5e-6);
+          bool good = rel <= (mode == TALOS_MODE_TF32 ? 2e-3 : 8e-6);   // (a wrong layout or a lost k-block shows as 1e-3 or more; the mode's contract is 1e-5)
           if (!good) { pass = false; if (dbg) { good = true; continue; } }
           for (int m = 0; m < LD && pass; ++m)                                               // nothing outside any member's [M,N]
             for (int n = ((m % member_rows) < M && m / member_rows < batch ? N : 0); n < LD; ++n) if (r1[(size_t)m * LD + n] != 0.f) { pass = false; break; }
@@ -507,12 +522,13 @@ bool self_check_shape(talos_ctx* ctx, const int M, const int N = 328, const int 
   return pass;
 }
 
-// Rows 200: one-CTA kernels; rows 456: the CTA-pair kernel (two 256-row tiles, the second one ragged); then a batch
+// Rows 200: one-CTA kernels; rows 456: the CTA-pair kernel (two 256-row tiles, the second one ragged; once more with a
+// reduction longer than one accumulation chain); then a batch
 // of three small ragged products (tiles must neither read nor write across batch members).
 bool self_check(talos_ctx* ctx) {
   bool ok = self_check_shape(ctx, 200) && self_check_shape(ctx, 72, 88, 104, 3);
   g_check_pair = true;
-  ok = ok && self_check_shape(ctx, 456);
+  ok = ok && self_check_shape(ctx, 456) && self_check_shape(ctx, 456, 328, 520);   // K = 520: two chains, folded on chip in 3xTF32 mode
   g_check_pair = false;
   return ok;
 }

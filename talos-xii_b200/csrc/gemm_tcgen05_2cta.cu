@@ -133,53 +133,76 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t a_lbo = A_MN ? BK * 128 : 16, b_lbo = B_MN ? BK * 128 : 16;
       const uint32_t a_kstep = A_MN ? 1024 : UMMA_K * 4, b_kstep = B_MN ? 1024 : UMMA_K * 4;
       const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024, a_lay = A_MN ? 1 : 2, b_lay = B_MN ? 1 : 2;
-      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
+      int stage = 0; uint32_t phase = 0; int tcount = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
       for (int it = pair; it < items && ok; it += npairs) {
         const int ks = it / tiles_mn;
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
-        if (!mbar_wait(tempty + acc, acc_phase[acc] ^ 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait((X3 ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
+        // The item's reduction runs as chains of chain_kb k-blocks: the first chain accumulates into the running
+        // buffer, every further one into the other buffer, which the epilogue warps fold into the running one.
+        const int run = tcount & 1; ++tcount;
+        const int ckb = g.chain_kb > 0 ? g.chain_kb : (kb1 - kb0);
+        for (int c0 = kb0; c0 < kb1 && ok; c0 += ckb) {
+          const int buf = (c0 == kb0) ? run : (run ^ 1), c1 = min(kb1, c0 + ckb);
+          if (!mbar_wait(tempty + buf, acc_phase[buf] ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          for (int kb = c0; kb < c1; ++kb) {
+            if (!mbar_wait((X3 ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
-            if (X3) {
-              const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
-              const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
-              tc_mma2_tf32(d_tmem, dal, db, idesc, accum);
-              tc_mma2_tf32(d_tmem, da, dbl, idesc, 1u);
-              tc_mma2_tf32(d_tmem, da, db, idesc, 1u);
-            } else {
-              tc_mma2_tf32(d_tmem, da, db, idesc, accum);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint32_t accum = (kb > c0 || k > 0) ? 1u : 0u;
+              const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
+              if (X3) {
+                const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
+                const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
+                tc_mma2_tf32(d_tmem, dal, db, idesc, accum);
+                tc_mma2_tf32(d_tmem, da, dbl, idesc, 1u);
+                tc_mma2_tf32(d_tmem, da, db, idesc, 1u);
+              } else {
+                tc_mma2_tf32(d_tmem, da, db, idesc, accum);
+              }
             }
+            tc_commit2(empty + stage);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          tc_commit2(empty + stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (!ok) break;
+          tc_commit2(tfull + buf);
+          acc_phase[buf] ^= 1;
         }
-        if (!ok) break;
-        tc_commit2(tfull + acc);
-        acc_phase[acc] ^= 1; acc ^= 1;
       }
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------- epilogue: each CTA drains its own 128 accumulator rows
     const uint32_t tempty_leader[2] = {map_to_cta(smem_u32(tempty + 0), 0), map_to_cta(smem_u32(tempty + 1), 0)};
-    int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
+    int tcount = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = pair; it < items && ok; it += npairs) {
       const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
-      if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
+      const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
+      const int run = tcount & 1, other = run ^ 1; ++tcount;
+      const int ckb = g.chain_kb > 0 ? g.chain_kb : (kb1 - kb0);
+      const uint32_t t_run = tmem_base + (uint32_t)(run * BN), t_other = tmem_base + (uint32_t)(other * BN);
+      // first chain: lands in the running buffer; nothing to do but to see it complete
+      if (!mbar_wait(tfull + run, acc_phase[run], abort_flag)) { ok = false; break; }
       tc_fence_after();
-      tc_epilogue_tile<BN>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32),
+      // further chains: fold each into the running buffer, then hand its buffer back to the issuer
+      for (int c0 = kb0 + ckb; c0 < kb1 && ok; c0 += ckb) {
+        if (!mbar_wait(tfull + other, acc_phase[other], abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        tc_fold_chain<BN>(t_run, t_other, warp);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader[other]);
+        acc_phase[other] ^= 1;
+      }
+      if (!ok) break;
+      tc_epilogue_tile<BN>(g, &tmap_c, t_run, warp, lane, stage_all + (warp - 2) * (32 * 32),
                            (long long)mb * 2 * BM + (long long)rank * BM, nb, ks, 0, store_count);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
-      acc_phase[acc] ^= 1; acc ^= 1;
+      if (lane == 0) mbar_arrive_cluster(tempty_leader[run]);
+      acc_phase[run] ^= 1;
     }
     if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();

@@ -15,6 +15,7 @@ struct TcArgs {
   int32_t* status;
   int tma_out;                             // 1: results leave through TMA stores (tmap_c), 0: direct stores
   int pf_a, pf_b;                          // prefetch this operand's tiles into L2 a few k-blocks ahead (large streamed operands only)
+  int chain_kb;                            // CTA-pair 3xTF32 kernel: k-blocks per accumulation chain folded on chip (0: one chain per item)
   int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
   long long stride_c;                      // elements between consecutive batch members of C
 };
@@ -112,6 +113,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+// 16-column forms for the on-chip fold of accumulation chains (running sum += finished chain, both in TMEM).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                 "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Round to TF32 (10 mantissa bits), nearest with ties away from zero -- the semantics of cvt.rna.tf32.f32 -- with two
 // integer operations on the bit pattern (add half an ulp of the kept part to the magnitude, clear the 13 dropped
@@ -200,6 +215,28 @@ __device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restri
 }
 
 
+
+// On-chip fold of one finished accumulation chain into the running sum: run[lane][col] += acc[lane][col] in fp32
+// (round to nearest), for this warp's TMEM lane quadrant and column half.  This is how the fp32-faithful mode keeps its
+// accumulation chains short (the tensor core truncates when it adds into the accumulator) without sending partial
+// tiles through memory.
+template <int BN>
+__device__ __forceinline__ void tc_fold_chain(uint32_t t_run, uint32_t t_acc, int warp) {
+  const int quad = warp & 3, half = (warp - 2) >> 2;
+  constexpr int HALF_COLS = BN >= 64 ? BN / 2 : BN;
+  const uint32_t row = (uint32_t)(quad * 32) << 16;
+#pragma unroll 1
+  for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 16) {
+    uint32_t a[16], r[16];
+    tmem_ld16(t_acc + row + (uint32_t)c0, a);
+    tmem_ld16(t_run + row + (uint32_t)c0, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(a[j]));
+    tmem_st16(t_run + row + (uint32_t)c0, r);
+  }
+  tmem_st_wait();
+}
 
 // One epilogue warp's share of a finished 128 x BN accumulator: warp w (2..9) owns TMEM lane quadrant w%4 (32 rows,
 // one per lane) and half of the columns, drained 32 columns at a time.  `t_base` is the TMEM address of the
