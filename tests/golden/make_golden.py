@@ -66,6 +66,22 @@ def build():
     p0 = n(47, (64,)); gr = n(48, (64,), 0.01); p = [p0.copy()]; m = [np.zeros(64)]; vv = [np.zeros(64)]
     for t in range(1, 4): om.adam_step(p, [orc.f32r(gr * t)], m, vv, t, np.float64(np.float32(3e-4)))
     g.update(adam_p0=p0, adam_g=gr, adam_p3=p[0])
+    # advantage block: reward normalisation + GAE + advantage normalisation (episode ends inside the buffer)
+    rw = orc.f32r(n(50, (300,)) * 3.0 + 1.0); va = n(51, (300,)); tm = (orc.rng_bounded(52, 300, 40) == 0).astype(np.int32)
+    adv, ret = orc.gae(rw, va, tm, 0.75, 2.25)
+    mean = orc.sum_f64(adv) / adv.size; std = np.sqrt(orc.sum_sq_diff(adv, mean) / adv.size) + 1e-8
+    g.update(gae_rewards=rw, gae_values=va, gae_terminals=tm, gae_adv=adv, gae_ret=ret, gae_norm=orc.normalize_slice(adv, mean, std))
+    # dueling double-DQN pieces at the crate's batch shape
+    dv_, da_ = n(53, (64, 1)), n(54, (64, 5)); dq = n(55, (64, 5))
+    qe, qt = n(56, (64, 5)), n(57, (64, 5)); r_ = n(58, (64,)); dn = (orc.rng_bounded(59, 64, 4) == 0).astype(np.float64); ac_ = orc.rng_bounded(60, 64, 5)
+    q_ = om.dueling_combine(dv_, da_); bdv, bda = om.dueling_combine_bwd(dq)
+    tg = om.dqn_target(qe, qt, r_, dn, np.float64(np.float32(0.99))); ls, ldq = om.dqn_loss_fwd_bwd(q_, ac_, tg)
+    g.update(dqn_v=dv_, dqn_a=da_, dqn_q=q_, dqn_dq=dq, dqn_bdv=bdv, dqn_bda=bda, dqn_qe=qe, dqn_qt=qt, dqn_r=r_, dqn_done=dn, dqn_actions=ac_,
+             dqn_target=tg, dqn_loss=np.array(ls), dqn_ldq=ldq)
+    # batched rollout: 5 simulations x 9 steps of the reference-sized policy, context 3, staggered episode ends
+    pol = om.ActorCritic(7)
+    st = n(61, (9, 5, 8), 0.5); rs = np.array([[1 if (t * 3 + s_) % 7 == 0 else 0 for s_ in range(5)] for t in range(9)])
+    g.update(roll_states=st, roll_resets=rs, roll_probs=om.rollout_reference(pol, st, rs, 3))
     return g
 
 

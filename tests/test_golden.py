@@ -94,4 +94,23 @@ def test_cuda_path_matches_golden_vectors(talos):
         gt = dev(orc.f32r(G["adam_g"] * t))
         L.talos_adam_step(ctx.handle, P(p), P(gt), P(m), P(vv), 64, t, 3e-4, 0.9, 0.999, 1e-8, 1.0, 0.0)
     ctx.synchronize(); assert rel_err(p, G["adam_p3"]) <= 1e-6
+    # advantage block
+    n = 300; rw, va = dev(G["gae_rewards"]), dev(G["gae_values"]); tm = torch.from_numpy(G["gae_terminals"].astype(np.int32)).cuda()
+    adv = e(n); ret = e(n); nrm = e(n)
+    L.talos_gae(ctx.handle, P(rw), P(va), P(tm), n, 0.99, 0.95, 0.75, 2.25, P(adv), P(ret))
+    L.talos_normalize_slice(ctx.handle, P(adv), n, P(nrm), None)
+    ctx.synchronize()
+    assert rel_err(adv, G["gae_adv"]) <= 1e-5 and rel_err(ret, G["gae_ret"]) <= 1e-5 and rel_err(nrm, G["gae_norm"]) <= 1e-5
+    # dueling double-DQN pieces
+    B, A = 64, 5
+    v_, a_, dq_ = dev(G["dqn_v"]), dev(G["dqn_a"]), dev(G["dqn_dq"]); q_ = e(B, A); bdv = e(B, 1); bda = e(B, A)
+    L.talos_dueling_combine_fwd(ctx.handle, P(v_), P(a_), P(q_), B, A)
+    L.talos_dueling_combine_bwd(ctx.handle, P(dq_), P(bdv), P(bda), B, A, 0)
+    qe, qt, r_, dn = dev(G["dqn_qe"]), dev(G["dqn_qt"]), dev(G["dqn_r"]), dev(G["dqn_done"]); tg = e(B)
+    L.talos_dqn_target(ctx.handle, P(qe), P(qt), P(r_), P(dn), 0.99, P(tg), B, A)
+    acts = torch.from_numpy(G["dqn_actions"].astype(np.int32)).cuda(); ls = e(1); ldq = e(B, A)
+    L.talos_dqn_loss_fwd_bwd(ctx.handle, P(q_), P(acts), P(tg), P(ls), P(ldq), B, A)
+    ctx.synchronize()
+    assert rel_err(q_, G["dqn_q"]) <= 1e-6 and rel_err(bdv, G["dqn_bdv"]) <= 1e-6 and rel_err(bda, G["dqn_bda"]) <= 1e-6
+    assert rel_err(tg, G["dqn_target"]) <= 1e-6 and abs(host(ls)[0] - float(G["dqn_loss"])) <= 1e-5 * float(G["dqn_loss"]) and rel_err(ldq, G["dqn_ldq"]) <= 1e-5
     ctx.close()

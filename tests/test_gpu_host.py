@@ -164,3 +164,14 @@ def test_batched_rollout_matches_per_simulation_cached_inference(mode, tol):
         top2 = np.sort(ref, -1)[..., -2:]
         clear = (top2[..., 1] - top2[..., 0]) > 1e-4
         assert np.array_equal(got.argmax(-1)[clear], ref.argmax(-1)[clear])
+
+
+def test_batched_rollout_with_the_crates_own_weights():
+    # the same comparison with the crate's own initialisation left as it is (half-range LCG: every weight negative),
+    # the reference's sizes (8 features, hidden 64, 5 actions), context 3, 5 simulations x 9 steps
+    seed, N, T, ctx_len = 7, 5, 9, 3
+    got = run_driver(["rollout", 1, seed, N, T, ctx_len], symmetric=False).reshape(T, N, 5)
+    states = nrm(seed + 500, (T, N, 8), 0.5)
+    resets = np.array([[1 if (t * 7 + n * 3) % 11 == 0 else 0 for n in range(N)] for t in range(T)])
+    ref = om.rollout_reference(om.ActorCritic(seed), states, resets, ctx_len)
+    assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 1e-5
