@@ -65,14 +65,39 @@ const char* talos_last_error_string(void);
 /* 1 when the tcgen05 tensor-core GEMM passed its start-up self-check on this ctx and is in use
  * for TF32 / TF32X3 modes; 0 when those modes are being served by the fp32 CUDA-core kernel. */
 int32_t talos_ctx_tensor_cores_active(talos_ctx* ctx);
+/* The same as a three-way answer: 1 = self-check passed, tensor cores in use; 0 = no product large enough to need them
+ * has run yet; -1 = the self-check FAILED and the fp32 kernel is standing in (results stay correct, speed does not). */
+int32_t talos_ctx_tensor_cores_state(talos_ctx* ctx);
 /* Number of kernels this library has launched on the ctx since creation. */
 int64_t talos_ctx_launch_count(talos_ctx* ctx);
+/* Test hook (no counterpart in the reference): writes `code` into the context's device-side error word from the
+ * host, exactly where a kernel whose bounded wait gave up (1000..2999) or that met an out-of-range index (3000)
+ * would write it.  The next entry point that blocks on the stream -- talos_ctx_synchronize, talos_copy_to_host,
+ * talos_download_f64, talos_ppo_get_params_host, talos_ppo_last_loss, talos_ppo_update[_host] -- must then return
+ * TALOS_ERR_TIMEOUT / TALOS_ERR_ARG and clear the word.  Lets the error path be tested without making a GPU misbehave. */
+talos_status talos_debug_set_device_status(talos_ctx* ctx, int32_t code);
+/* Test hook (no counterpart in the reference): makes a bounded wait inside the tensor-core GEMM kernel run out, the
+ * way a lost copy would, WITHOUT faulting, trapping or hanging anything.  While skip_k_block >= 0, the first CTA of
+ * every one-CTA tensor-core GEMM launched on this ctx leaves out the loads of that k-block (32 reduction elements) of
+ * its first tile; the roles waiting for it poll `wait_spins` times (0 = the default 2^22, a few seconds; tests pass a
+ * small value, >= 1024), give up, raise the device error word, let copies in flight land, free their tensor memory
+ * and return.  The affected tile's results are undefined; the next blocking entry point returns TALOS_ERR_TIMEOUT.
+ * skip_k_block = -1, wait_spins = 0 restores normal operation. */
+talos_status talos_debug_gemm_stall(talos_ctx* ctx, int32_t skip_k_block, uint32_t wait_spins);
 
 /* ---- device memory for hosts without a CUDA runtime binding of their own (the storage behind
  * Tensor.data / Tensor.grad, src/autograd.rs:15-20).  Copies are ordered on the ctx stream; the
  * *_host copies block until the host buffer may be reused / holds the data. */
+/* talos_malloc / talos_free go through a per-context caching allocator (size classes: powers of two up to 1 MiB,
+ * then multiples of 1 MiB): the reference allocates a fresh result and gradient buffer per op
+ * (src/autograd.rs:94-107), so in steady state neither call reaches the CUDA driver or synchronises.  A freed block
+ * is handed only to later work on the same ctx stream.  talos_free refuses a pointer it did not hand out. */
 talos_status talos_malloc(talos_ctx* ctx, size_t bytes, void** out);
 talos_status talos_free(talos_ctx* ctx, void* ptr);
+/* Returns the allocator's idle blocks to the driver (waits for the stream first). */
+talos_status talos_ctx_trim(talos_ctx* ctx);
+/* stats4_host = {bytes handed out, bytes idle in the cache, cudaMalloc calls made, requests served from the cache}. */
+talos_status talos_ctx_memory_stats(talos_ctx* ctx, int64_t* stats4_host);
 talos_status talos_memset_zero(talos_ctx* ctx, void* ptr, size_t bytes);
 talos_status talos_copy_from_host(talos_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 talos_status talos_copy_to_host(talos_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
@@ -132,14 +157,30 @@ talos_status talos_colsum(talos_ctx* ctx, const float* g, float* out, int64_t ro
  * has no device memory to manage).  talos_colsum takes its partial-sum scratch from the context and may
  * grow it with cudaMalloc, which synchronises the whole device: a trainer thread doing that stalls every
  * other thread's kernels, and a host that gave all device memory to its own pool has none left to hand out.
- * This variant keeps the scratch in a fixed 2 MiB array inside the library image (each GPU that loads the
- * library holds it until the process exits) and never allocates or frees anything.
+ * This variant keeps the scratch in a fixed 2 MiB array inside the library image and never allocates or
+ * frees anything.  Each GPU on which a context has been created (or this function called) holds the array
+ * until the process exits: talos_ctx_create looks up the array's device address, which is the moment the
+ * driver loads the module and sets the 2 MiB aside -- so create the context at start-up, before the
+ * allocation-free phase of the caller begins and before any stream capture.  If that look-up failed, the
+ * first call repeats it (and may then allocate, once).
  * Limits: n <= 1024 columns; wider input is refused with TALOS_ERR_UNSUPPORTED.
- * The first call on a device looks up the array's device address; make that call before starting any
- * stream capture.  All calls share the one array: two calls whose kernels overlap on the GPU (different
- * streams or contexts) race on it, so keep them on one stream or serialise them.  Nothing in the array has
- * to be cleared between calls: each call overwrites every element it later reads. */
+ * All calls share the one array: two calls whose kernels overlap on the GPU (different streams or
+ * contexts) race on it, so keep them on one stream or serialise them.  Nothing in the array has to be
+ * cleared between calls: each call overwrites every element it later reads. */
 talos_status talos_colsum_noalloc(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n, int32_t accumulate);
+
+/* ---- the slice primitives of src/simd.rs on device vectors ----------------------------------- */
+/* add_scaled_row (src/simd.rs:2-32): out[i] += scale * row[i]. */
+talos_status talos_axpy(talos_ctx* ctx, float* out, const float* row, float scale, int64_t n);
+/* dot_product (src/simd.rs:34-63): out[0] (+)= sum_i a[i] * b[i]; out is a device scalar. */
+talos_status talos_dot(talos_ctx* ctx, const float* a, const float* b, int64_t n, float* out, int32_t accumulate);
+/* vector_fma (src/simd.rs:66-94): dst[i] += a[i] * b[i]. */
+talos_status talos_vector_fma(talos_ctx* ctx, float* dst, const float* a, const float* b, int64_t n);
+/* vector_scale (src/simd.rs:362-379): row[i] *= scale. */
+talos_status talos_vector_scale(talos_ctx* ctx, float* row, float scale, int64_t n);
+/* softmax_exp_sum (src/simd.rs:333-359): row[i] = exp(row[i] - max(row)) in place, sum_out[0] (device) = their sum;
+ * an empty row gives 0. */
+talos_status talos_softmax_exp_sum(talos_ctx* ctx, float* row, int64_t n, float* sum_out);
 
 /* ---- RMSNorm (src/nn.rs:145-304): rms = sqrt(mean(x^2)+eps), y = x/rms*gamma --------------- */
 /* inv_rms [rows] is the only thing saved for backward (x-hat is recomputed). */
@@ -166,7 +207,7 @@ talos_status talos_rope(talos_ctx* ctx, const float* x, float* y, const float* c
 
 /* ---- softmax (src/transformer.rs:1052-1121; src/simd.rs:333-359) -------------------------- */
 /* y = softmax(scale * x) over rows of length len.  causal_period > 0 (not in the reference):
- * row r sees columns j <= r % causal_period. */
+ * row r sees columns j <= r % causal_period; 0 <= causal_period <= len, anything else is TALOS_ERR_SHAPE. */
 talos_status talos_softmax_fwd(talos_ctx* ctx, const float* x, float* y, int64_t rows, int64_t len, float scale,
                                int64_t causal_period);
 /* dx (+)= scale * y * (dy - sum_j dy_j y_j). */

@@ -50,6 +50,9 @@ talos_status talos_ppo_destroy(talos_ppo* p);
 talos_status talos_ppo_param_count(talos_ppo* p, int64_t* n_out);
 talos_status talos_ppo_set_params_host(talos_ppo* p, const float* flat_host);
 talos_status talos_ppo_get_params_host(talos_ppo* p, float* flat_host);
+/* The gradient the last optimizer step applied: d(mean loss)/d(parameter) over the samples of all ranks, in the same
+ * canonical order (what Tensor.grad holds after loss.backward(), src/ppo.rs:756-758).  Blocks. */
+talos_status talos_ppo_get_grads_host(talos_ppo* p, float* flat_host);
 /* Resets the Adam moments and the step counter (Adam::new, src/ppo.rs:494-513). */
 talos_status talos_ppo_reset_optimizer(talos_ppo* p);
 talos_status talos_ppo_set_lr(talos_ppo* p, float lr);

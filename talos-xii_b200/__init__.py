@@ -114,7 +114,7 @@ class _Lib:
         return checked
 
 
-_NOT_STATUS = {"talos_ctx_tensor_cores_active"}
+_NOT_STATUS = {"talos_ctx_tensor_cores_active", "talos_ctx_tensor_cores_state"}
 
 lib = _Lib()
 
@@ -154,6 +154,11 @@ class Context:
     @property
     def tensor_cores_active(self):
         return bool(lib.talos_ctx_tensor_cores_active(self.handle))
+
+    @property
+    def tensor_cores_state(self):
+        """1: in use; 0: not probed yet; -1: the start-up self-check failed and the fp32 kernel serves every mode."""
+        return int(lib.talos_ctx_tensor_cores_state(self.handle))
 
     def __del__(self):
         try:
@@ -243,6 +248,20 @@ class PPOTrainer:
         for k, shp in zip(self.NAMES, self._shapes()):
             n = int(np.prod(shp)); out[k] = flat[o:o + n].reshape(shp); o += n
         return out
+
+    def _split(self, flat):
+        import numpy as np
+        out, o = {}, 0
+        for k, shp in zip(self.NAMES, self._shapes()):
+            n = int(np.prod(shp)); out[k] = flat[o:o + n].reshape(shp); o += n
+        return out
+
+    def get_grads(self):
+        """Mean gradient of the last optimizer step (all ranks), as a dict in the canonical order."""
+        import numpy as np
+        flat = np.empty(self.n_params, dtype=np.float32)
+        lib.talos_ppo_get_grads_host(self.handle, ptr(flat))
+        return self._split(flat)
 
     def reset_optimizer(self):
         lib.talos_ppo_reset_optimizer(self.handle)

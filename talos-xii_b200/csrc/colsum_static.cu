@@ -5,8 +5,10 @@
 // trainer thread that calls it stalls the kernels of every other thread sharing the GPU (the reference
 // runs trainers and simulators side by side, src/main.rs:580-721), and a host that has handed all device
 // memory to its own pool may have nothing left for the driver to give.  For them this file keeps the
-// scratch in a fixed array that is part of the loaded module: every GPU that loads the library holds
-// these 2 MiB until the process exits, and nothing is ever allocated or freed by the call.
+// scratch in a fixed array that is part of the loaded module: every GPU on which a context is created
+// (or this entry point is called) holds these 2 MiB until the process exits.  The array's address is
+// resolved when a context is created on the device -- that is when the driver loads the module and sets
+// the array aside -- so the calls themselves never allocate or free anything.
 #include <mutex>
 
 #include "common.cuh"
@@ -58,6 +60,13 @@ __global__ void static_colsum_stage2(const float* __restrict__ scratch, int slab
 }
 
 }  // namespace
+
+// Called by talos_ctx_create with `device` current: the lookup loads this file's module on the device, which is when
+// the driver sets the array's 2 MiB aside, so it happens at start-up rather than inside the first call of a thread
+// that must not wait for an allocation.  A failure here is not fatal: the entry point repeats the lookup and reports it.
+void talos_colsum_noalloc_prepare(int device) {
+  try { scratch_for_current_device(device); } catch (const talos_error&) { cudaGetLastError(); }
+}
 
 TALOS_API talos_status talos_colsum_noalloc(talos_ctx* ctx, const float* g, float* out, int64_t rows, int64_t n,
                                             int32_t accumulate) {

@@ -49,11 +49,25 @@ struct talos_ctx {
   size_t ws_bytes = 0;
   void* ws2 = nullptr;         // op-level scratch of composite entry points: dZ of Linear backward, dS of attention
   size_t ws2_bytes = 0;
-  int32_t* dev_status = nullptr;   // device-side error word written by bounded waits
+  int32_t* dev_status = nullptr;   // device-side error word: 1000..2999 a bounded wait gave up, 3000 an index argument was out of range
+  int32_t* host_status = nullptr;  // pinned host copy, refreshed by every entry point that blocks on the stream
   int tc_state = 0;            // tensor-core GEMM: 0 = not probed, 1 = active, -1 = disabled
   std::atomic<int64_t> launches{0};
-  void* tmap_cache = nullptr;  // owned by gemm_tcgen05.cu
+  unsigned dbg_wait_spins = 0;     // test hook (talos_debug_gemm_stall): poll limit of the GEMM kernels' bounded waits, 0 = default
+  int dbg_skip_kb = -1;            // test hook: k-block the first CTA's loader leaves out, -1 = none
+  struct talos_pool* pool = nullptr;   // caching device allocator behind talos_malloc / talos_free (ctx.cu)
 };
+
+// Device-side error codes written to talos_ctx::dev_status (first writer wins is not required: any non-zero value reports).
+#define TALOS_DEV_TIMEOUT_BASE 1000    // + CTA index % 1000 (+ 1000 from the CTA-pair kernel): a bounded mbarrier / flag wait gave up  -> TALOS_ERR_TIMEOUT
+#define TALOS_DEV_BAD_INDEX 3000       // an action / index argument read from device memory was out of range -> TALOS_ERR_ARG
+
+// Blocks until the ctx stream is idle, then reports (and clears) the device-side error word: every entry point that
+// already waits for the stream calls this instead of cudaStreamSynchronize, so a kernel that gave up is never followed
+// by a silent TALOS_OK.
+void talos_sync_and_check(talos_ctx* ctx);
+// Looks up the device address of talos_colsum_noalloc's fixed scratch array for `device` (which must be current).
+void talos_colsum_noalloc_prepare(int device);
 
 // Returns a scratch pointer of at least `bytes`, growing the buffer (stream-ordered free of the
 // old one) when needed.
@@ -155,4 +169,3 @@ bool talos_dact_colsum_launch(talos_ctx* ctx, const float* dy, float* dz, const 
 bool talos_gemm_tc_launch_batched(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                   int64_t strideA, const float* B, int64_t ldb, int64_t strideB, float* C, int64_t ldc, int64_t strideC,
                                   int64_t batch, int mode, const EpiArgs& epi);
-void talos_gemm_tc_release(talos_ctx* ctx);

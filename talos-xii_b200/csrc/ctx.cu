@@ -2,6 +2,10 @@
 #include <math.h>
 #include <string.h>
 
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
 #include "common.cuh"
 
 static thread_local std::string g_last_error;
@@ -23,6 +27,49 @@ static void* grow_scratch(talos_ctx* ctx, void** buf, size_t* have, size_t bytes
 void* talos_workspace(talos_ctx* ctx, size_t bytes) { return grow_scratch(ctx, &ctx->ws, &ctx->ws_bytes, bytes); }
 void* talos_workspace2(talos_ctx* ctx, size_t bytes) { return grow_scratch(ctx, &ctx->ws2, &ctx->ws2_bytes, bytes); }
 
+// ---- caching device allocator -----------------------------------------------------------------------------------
+// The reference allocates a fresh result (and a fresh gradient buffer) for every op (src/autograd.rs:94-107), so the
+// host mirror above this ABI asks for device memory thousands of times per training step.  cudaMalloc / cudaFree cost
+// tens of microseconds and cudaFree synchronises the device; blocks are therefore kept per context in free lists by
+// size class and handed out again without touching the driver.  A block freed by the host may still be read by work
+// already enqueued, and is only ever handed to work enqueued LATER on the same stream (one ctx = one stream), so reuse
+// needs no synchronisation.  Size classes: powers of two up to 1 MiB, then multiples of 1 MiB.
+struct talos_pool {
+  std::mutex mu;
+  std::unordered_map<size_t, std::vector<void*>> free_lists;       // class size -> idle blocks
+  std::unordered_map<void*, size_t> live;                          // block -> class size
+  size_t cached_bytes = 0, live_bytes = 0;
+  int64_t driver_allocs = 0, reuses = 0;
+  static size_t size_class(size_t bytes) {
+    if (bytes <= 256) return 256;
+    if (bytes <= (size_t(1) << 20)) { size_t c = 256; while (c < bytes) c <<= 1; return c; }
+    return (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+  }
+};
+
+// Returns every idle block to the driver (after the stream has drained: an idle block may still be read by queued work).
+static void pool_trim(talos_ctx* ctx) {
+  talos_pool* pl = ctx->pool;
+  if (!pl || pl->cached_bytes == 0) return;
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& kv : pl->free_lists) { for (void* p : kv.second) cudaFree(p); kv.second.clear(); }
+  pl->cached_bytes = 0;
+}
+
+void talos_sync_and_check(talos_ctx* ctx) {
+  // the status word rides along with the wait the caller needs anyway: one 4-byte copy enqueued before the sync
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  const int32_t st = *ctx->host_status;
+  if (st != 0) {
+    *ctx->host_status = 0;
+    TALOS_CHECK_CUDA(cudaMemsetAsync(ctx->dev_status, 0, 64, ctx->stream));
+    if (st >= TALOS_DEV_BAD_INDEX)
+      throw talos_error(TALOS_ERR_ARG, "an index read from device memory was out of range (an action outside [0, n_actions)); the kernel skipped it (status " + std::to_string(st) + ")");
+    throw talos_error(TALOS_ERR_TIMEOUT, "a bounded device-side wait gave up (status " + std::to_string(st) + ")");
+  }
+}
+
 TALOS_API talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx** out) {
   TALOS_ENTRY_BEGIN
   TALOS_REQUIRE(out != nullptr, TALOS_ERR_ARG, "null out pointer");
@@ -39,6 +86,10 @@ TALOS_API talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx*
   c->stream = (cudaStream_t)stream; c->own_stream = false;     // NULL is the device's default stream
   TALOS_CHECK_CUDA(cudaMalloc(&c->dev_status, 64));
   TALOS_CHECK_CUDA(cudaMemset(c->dev_status, 0, 64));
+  TALOS_CHECK_CUDA(cudaMallocHost(&c->host_status, 64));
+  memset(c->host_status, 0, 64);
+  c->pool = new talos_pool();
+  talos_colsum_noalloc_prepare(device);     // resolve the fixed scratch array's address now, not inside a trainer thread's first call
   *out = c;
   TALOS_ENTRY_END
 }
@@ -48,7 +99,12 @@ TALOS_API talos_status talos_ctx_destroy(talos_ctx* ctx) {
   if (!ctx) return TALOS_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
-  talos_gemm_tc_release(ctx);
+  if (ctx->pool) {
+    pool_trim(ctx);
+    for (auto& kv : ctx->pool->live) cudaFree(kv.first);          // blocks the host never returned
+    delete ctx->pool;
+  }
+  if (ctx->host_status) cudaFreeHost(ctx->host_status);
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->ws2) cudaFree(ctx->ws2);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
@@ -60,13 +116,23 @@ TALOS_API talos_status talos_ctx_destroy(talos_ctx* ctx) {
 TALOS_API talos_status talos_ctx_synchronize(talos_ctx* ctx) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
+  talos_sync_and_check(ctx);
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_debug_set_device_status(talos_ctx* ctx, int32_t code) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(ctx->dev_status, &code, sizeof(code), cudaMemcpyHostToDevice, ctx->stream));
   TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
-  int32_t st = 0;
-  TALOS_CHECK_CUDA(cudaMemcpy(&st, ctx->dev_status, sizeof(st), cudaMemcpyDeviceToHost));
-  if (st != 0) {
-    cudaMemset(ctx->dev_status, 0, 64);
-    throw talos_error(TALOS_ERR_TIMEOUT, "a bounded device-side wait gave up (status " + std::to_string(st) + ")");
-  }
+  TALOS_ENTRY_END
+}
+
+TALOS_API talos_status talos_debug_gemm_stall(talos_ctx* ctx, int32_t skip_k_block, uint32_t wait_spins) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(skip_k_block >= -1 && (wait_spins == 0 || wait_spins >= 1024), TALOS_ERR_ARG, "bad stall parameters");
+  ctx->dbg_skip_kb = skip_k_block; ctx->dbg_wait_spins = wait_spins;
   TALOS_ENTRY_END
 }
 
@@ -88,6 +154,7 @@ TALOS_API talos_status talos_ctx_reserve_workspace(talos_ctx* ctx, size_t bytes)
 }
 
 TALOS_API int32_t talos_ctx_tensor_cores_active(talos_ctx* ctx) { return ctx && ctx->tc_state == 1 ? 1 : 0; }
+TALOS_API int32_t talos_ctx_tensor_cores_state(talos_ctx* ctx) { return ctx ? ctx->tc_state : 0; }
 TALOS_API int64_t talos_ctx_launch_count(talos_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
 
 // ---- device memory for hosts that bind only this ABI ----
@@ -97,14 +164,53 @@ TALOS_API talos_status talos_malloc(talos_ctx* ctx, size_t bytes, void** out) {
   TALOS_REQUIRE(out != nullptr, TALOS_ERR_ARG, "null out pointer");
   *out = nullptr;
   if (bytes == 0) return TALOS_OK;
-  cudaError_t e = cudaMalloc(out, bytes);
-  if (e != cudaSuccess) { cudaGetLastError(); throw talos_error(TALOS_ERR_ALLOC, "device allocation failed"); }
+  talos_pool* pl = ctx->pool;
+  const size_t cls = talos_pool::size_class(bytes);
+  std::lock_guard<std::mutex> lock(pl->mu);
+  auto it = pl->free_lists.find(cls);
+  void* p = nullptr;
+  if (it != pl->free_lists.end() && !it->second.empty()) {
+    p = it->second.back(); it->second.pop_back(); pl->cached_bytes -= cls; pl->reuses += 1;
+  } else {
+    cudaError_t e = cudaMalloc(&p, cls);
+    if (e != cudaSuccess) {                                         // give the idle blocks back to the driver and try once more
+      cudaGetLastError(); pool_trim(ctx);
+      e = cudaMalloc(&p, cls);
+      if (e != cudaSuccess) { cudaGetLastError(); throw talos_error(TALOS_ERR_ALLOC, "device allocation failed"); }
+    }
+    pl->driver_allocs += 1;
+  }
+  pl->live[p] = cls; pl->live_bytes += cls;
+  *out = p;
   TALOS_ENTRY_END
 }
 TALOS_API talos_status talos_free(talos_ctx* ctx, void* ptr) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
-  if (ptr) { TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream)); TALOS_CHECK_CUDA(cudaFree(ptr)); }
+  if (!ptr) return TALOS_OK;
+  talos_pool* pl = ctx->pool;
+  std::lock_guard<std::mutex> lock(pl->mu);
+  auto it = pl->live.find(ptr);
+  TALOS_REQUIRE(it != pl->live.end(), TALOS_ERR_ARG, "talos_free: pointer was not returned by talos_malloc on this context");
+  const size_t cls = it->second;
+  pl->live.erase(it); pl->live_bytes -= cls;
+  pl->free_lists[cls].push_back(ptr); pl->cached_bytes += cls;
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ctx_trim(talos_ctx* ctx) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  std::lock_guard<std::mutex> lock(ctx->pool->mu);
+  pool_trim(ctx);
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ctx_memory_stats(talos_ctx* ctx, int64_t* stats4) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(stats4 != nullptr, TALOS_ERR_ARG, "null pointer");
+  std::lock_guard<std::mutex> lock(ctx->pool->mu);
+  stats4[0] = (int64_t)ctx->pool->live_bytes; stats4[1] = (int64_t)ctx->pool->cached_bytes;
+  stats4[2] = ctx->pool->driver_allocs; stats4[3] = ctx->pool->reuses;
   TALOS_ENTRY_END
 }
 TALOS_API talos_status talos_memset_zero(talos_ctx* ctx, void* ptr, size_t bytes) {
@@ -129,7 +235,7 @@ TALOS_API talos_status talos_copy_to_host(talos_ctx* ctx, void* dst, const void*
   if (bytes) {
     TALOS_REQUIRE(dst && src, TALOS_ERR_ARG, "null pointer");
     TALOS_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-    TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    talos_sync_and_check(ctx);
   }
   TALOS_ENTRY_END
 }
@@ -162,7 +268,7 @@ TALOS_API talos_status talos_download_f64(talos_ctx* ctx, double* dst, const flo
   std::string buf(sizeof(float) * (size_t)n, '\0');
   float* f = (float*)&buf[0];
   TALOS_CHECK_CUDA(cudaMemcpyAsync(f, src, sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost, ctx->stream));
-  TALOS_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+  talos_sync_and_check(ctx);
   for (int64_t i = 0; i < n; ++i) dst[i] = (double)f[i];
   TALOS_ENTRY_END
 }

@@ -41,11 +41,16 @@ __global__ void dqn_target_kernel(const float* __restrict__ q_eval, const float*
 // One block; partial sums are combined in thread order, so the loss is reproducible.
 __global__ void __launch_bounds__(256)
 dqn_loss_kernel(const float* __restrict__ q, const int32_t* __restrict__ actions, const float* __restrict__ target, float* __restrict__ loss,
-                float* __restrict__ dq, long long B, int A) {
+                float* __restrict__ dq, long long B, int A, int32_t* __restrict__ status) {
   __shared__ double sh[256];
   double acc = 0.0;
   for (long long b = threadIdx.x; b < B; b += 256) {
     const int act = actions[b];
+    if (act < 0 || act >= A) {                         // a stale action buffer must not become a wild read: skip the sample, report it
+      atomicExch(status, TALOS_DEV_BAD_INDEX);
+      if (dq) for (int a = 0; a < A; ++a) dq[b * A + a] = 0.f;
+      continue;
+    }
     const float d = q[b * A + act] - target[b];
     acc += (double)d * d;
     if (dq) for (int a = 0; a < A; ++a) dq[b * A + a] = (a == act) ? 2.f * d / (float)B : 0.f;
@@ -102,7 +107,7 @@ TALOS_API talos_status talos_dqn_loss_fwd_bwd(talos_ctx* ctx, const float* q, co
   talos_check_ctx(ctx);
   TALOS_REQUIRE(B >= 1 && A >= 1 && A <= 4096, TALOS_ERR_SHAPE, "bad DQN loss shape");
   TALOS_REQUIRE(q && actions && target && loss, TALOS_ERR_ARG, "null pointer");
-  dqn_loss_kernel<<<1, 256, 0, ctx->stream>>>(q, actions, target, loss, dq, B, (int)A);
+  dqn_loss_kernel<<<1, 256, 0, ctx->stream>>>(q, actions, target, loss, dq, B, (int)A, ctx->dev_status);
   talos_launched(ctx, "dqn_loss");
   TALOS_ENTRY_END
 }

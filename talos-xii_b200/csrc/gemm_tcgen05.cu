@@ -68,7 +68,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, CONV_WARPS ? CONV_WARPS : 1); mbar_init(empty + s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, EPI_WARPS); }
-    *abort_flag = 0;
+    abort_flag[0] = 0; abort_flag[1] = (int)g.wait_spins;
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -118,6 +118,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int kb = kb0; kb < kb1; ++kb) {
           if (pf_on) pf_step();
           if (!mbar_wait(empty + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+          // Test hook: this stage is never armed nor loaded, so its consumers' bounded waits run out and the CTA
+          // leaves through the abort path (nothing faults; the loads already in flight land and are ignored).
+          if (g.dbg_skip_kb >= 0 && blockIdx.x == 0 && it == 0 && kb - kb0 == g.dbg_skip_kb) { if (++stage == STAGES) { stage = 0; phase ^= 1; } continue; }
           mbar_expect_tx(full + stage, A_BYTES + B_BYTES + (BPS ? B_BYTES : 0));
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
           if (BPS) {
@@ -227,7 +230,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   if (*abort_flag) {
     // A wait gave up: report it, give copies still in flight time to land, then release TMEM.
-    if (threadIdx.x == 0) atomicExch(g.status, 1000 + (int)blockIdx.x % 1000);
+    if (threadIdx.x == 0) atomicExch(g.status, TALOS_DEV_TIMEOUT_BASE + (int)blockIdx.x % 1000);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
@@ -342,6 +345,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
+  g.wait_spins = ctx->dbg_wait_spins ? ctx->dbg_wait_spins : WAIT_SPINS; g.dbg_skip_kb = ctx->dbg_skip_kb;
   // Streamed K-major operands (more than 8 MB, i.e. not something that stays in L2 anyway) of the 3xTF32 kernels are
   // prefetched into L2 ahead of the loads: those kernels have only two or three stages in flight.  Measured on
   // 65 536 x 256 x 256: 3xTF32 A.B 65.0 -> 59.7 us, A.B^T 63.4 -> 59.3 us; the TF32 kernels (four or more stages)
@@ -358,7 +362,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // They also need enough 256 x 256 tiles to occupy every CTA pair without splitting K (the split-K weight-gradient
   // shapes have one or two tiles and are faster on 148 independent CTAs than on 74 pairs).
   const bool pair_shape = K >= 1024 && ceil_div(M, 2 * BM) * ceil_div(N, 256) >= ctx->sm_count / 2;
-  const bool pair = !batched && bn == 256 && M >= 256 && (pair_shape || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
+  const bool pair = ctx->dbg_skip_kb < 0 && !batched && bn == 256 && M >= 256 && (pair_shape || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
   g.m_tiles = (int)ceil_div(M, pair ? 2 * BM : BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
   int tiles = g.m_tiles * g.n_tiles, splits = 1;
   const int workers = pair ? ctx->sm_count / 2 : ctx->sm_count;   // CTAs, or CTA pairs
@@ -575,5 +579,3 @@ bool talos_gemm_tc_launch_batched(talos_ctx* ctx, int opA, int opB, int64_t M, i
   tc_launch(ctx, opA, opB, M, N, K, A, lda, B, ldb, C, ldc, mode, epi, TcBatch{batch, strideA, strideB, strideC});
   return true;
 }
-
-void talos_gemm_tc_release(talos_ctx*) {}

@@ -84,7 +84,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, 8); mbar_init(empty + s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, 16); }
-    *abort_flag = 0;
+    abort_flag[0] = 0; abort_flag[1] = (int)g.wait_spins;
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc2(tmem_slot, TMEM_COLS); tmem_relinquish2(); }
@@ -238,7 +238,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
-    if (threadIdx.x == 0) atomicExch(g.status, 2000 + (int)blockIdx.x % 1000);
+    if (threadIdx.x == 0) atomicExch(g.status, TALOS_DEV_TIMEOUT_BASE + 1000 + (int)blockIdx.x % 1000);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }

@@ -15,7 +15,7 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
                 const int* __restrict__ actions, const float* __restrict__ old_logp, const float* __restrict__ adv,
                 const float* __restrict__ ret, long long n, int n_actions, float clip, float c_v, float c_h, float inv_denom,
                 float* __restrict__ dlogits, long long ld_out, float* __restrict__ dvalues, long long dvs,
-                float* __restrict__ partial, int vec) {
+                float* __restrict__ partial, int vec, int32_t* __restrict__ status) {
   __shared__ float sh_loss[128], sh_kl[128];
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   float loss = 0.f, kl = 0.f;
@@ -42,6 +42,9 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
     for (int a = 0; a < na; ++a) se += expf(l[a] - mx);
     const float lse = logf(se) + mx;
     const int act = actions[i];
+    // An action outside [0, na) would match no logit below and yield a plausible-looking loss: report it instead
+    // (the sample then contributes its entropy and value terms only).
+    if (act < 0 || act >= na) atomicExch(status, TALOS_DEV_BAD_INDEX);
     const float advantage = adv[i];
     float ent = 0.f, lp_a = 0.f, sum_d = 0.f;
 #pragma unroll
@@ -152,7 +155,7 @@ TALOS_API talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logit
   TALOS_REQUIRE(logits && values && actions && old_logp && adv && ret && dlogits && dvalues && stats, TALOS_ERR_ARG, "null pointer");
   int blocks = (int)ceil_div(n, 128);
   float* partial = (float*)talos_workspace(ctx, sizeof(float) * 2 * (size_t)blocks);
-#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial, vec)
+#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial, vec, ctx->dev_status)
   const int vec = (((uintptr_t)logits | (uintptr_t)dlogits) & 15) == 0 && ld_logits % 4 == 0 && ld_out % 4 == 0;
   if (n_actions == 16) TALOS_PPO_LAUNCH(16); else if (n_actions == 5) TALOS_PPO_LAUNCH(5); else TALOS_PPO_LAUNCH(0);
 #undef TALOS_PPO_LAUNCH

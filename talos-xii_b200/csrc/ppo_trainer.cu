@@ -109,13 +109,16 @@ __global__ void unpack_heads_kernel(const float* __restrict__ z, int HP, int A, 
   float v = z[r * HP + c];
   if (c < A) { if (logits) logits[r * A + c] = v; } else if (values) values[r] = v;
 }
-__global__ void log_prob_kernel(const float* __restrict__ z, int HP, int A, const int* __restrict__ actions, long long n, float* __restrict__ out) {
+__global__ void log_prob_kernel(const float* __restrict__ z, int HP, int A, const int* __restrict__ actions, long long n, float* __restrict__ out,
+                                int32_t* __restrict__ status) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float* l = z + i * HP; float mx = -INFINITY;
   for (int a = 0; a < A; ++a) mx = fmaxf(mx, l[a]);
   float se = 0.f; for (int a = 0; a < A; ++a) se += expf(l[a] - mx);
-  out[i] = l[actions[i]] - (logf(se) + mx);
+  const int act = actions[i];
+  if (act < 0 || act >= A) { atomicExch(status, TALOS_DEV_BAD_INDEX); out[i] = 0.f; return; }   // no read outside the row; reported at the next sync
+  out[i] = l[act] - (logf(se) + mx);
 }
 
 void forward(talos_ppo* p, const float* obs, int64_t n) {
@@ -251,7 +254,7 @@ void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* act
     // mean approx-KL of the epoch (src/ppo.rs:729-731, :762-767): the step's device->host read
     stats.resize(4 * (size_t)p->steps_in_epoch);
     TALOS_CHECK_CUDA(cudaMemcpyAsync(stats.data(), p->step_stats, stats.size() * sizeof(float), cudaMemcpyDeviceToHost, p->ctx->stream));
-    TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+    talos_sync_and_check(p->ctx);        // a kernel that gave up (or met a bad action) ends the update here: no further epochs on garbage gradients
     double kl = 0, cnt = 0;
     for (int64_t i = 0; i < p->steps_in_epoch; ++i) { kl += stats[4 * i + 1]; cnt += stats[4 * i + 2]; }
     float mean_kl = cnt > 0 ? (float)(kl / cnt) : 0.f;
@@ -338,7 +341,19 @@ TALOS_API talos_status talos_ppo_get_params_host(talos_ppo* p, float* flat) {
   check(p); TALOS_REQUIRE(flat != nullptr, TALOS_ERR_ARG, "null pointer");
   p->host_tmp.resize((size_t)p->n_int);
   TALOS_CHECK_CUDA(cudaMemcpyAsync(p->host_tmp.data(), p->params, sizeof(float) * (size_t)p->n_int, cudaMemcpyDeviceToHost, p->ctx->stream));
-  TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  talos_sync_and_check(p->ctx);
+  unpack_params(p, p->host_tmp.data(), flat);
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ppo_get_grads_host(talos_ppo* p, float* flat) {
+  TALOS_ENTRY_BEGIN
+  check(p); TALOS_REQUIRE(flat != nullptr, TALOS_ERR_ARG, "null pointer");
+  TALOS_REQUIRE(p->t > 0, TALOS_ERR_ARG, "no optimizer step has run");
+  p->host_tmp.resize((size_t)p->n_int + 4);
+  TALOS_CHECK_CUDA(cudaMemcpyAsync(p->host_tmp.data(), p->grads, sizeof(float) * (size_t)(p->n_int + 4), cudaMemcpyDeviceToHost, p->ctx->stream));
+  talos_sync_and_check(p->ctx);
+  const float count = std::max(p->host_tmp[(size_t)p->n_int + 2], 1.f);       // the buffer holds sums over the samples of all ranks
+  for (int64_t i = 0; i < p->n_int; ++i) p->host_tmp[(size_t)i] /= count;
   unpack_params(p, p->host_tmp.data(), flat);
   TALOS_ENTRY_END
 }
@@ -377,7 +392,7 @@ TALOS_API talos_status talos_ppo_log_prob(talos_ppo* p, const float* obs, const 
   for (int64_t s = 0; s < n; s += c.minibatch) {
     int64_t m = std::min<int64_t>(c.minibatch, n - s);
     forward(p, obs + s * c.obs_dim, m);
-    log_prob_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, p->ctx->stream>>>(p->z, p->HP, c.n_actions, actions + s, m, out + s);
+    log_prob_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, p->ctx->stream>>>(p->z, p->HP, c.n_actions, actions + s, m, out + s, p->ctx->dev_status);
     talos_launched(p->ctx, "log_prob");
   }
   TALOS_ENTRY_END
@@ -450,7 +465,7 @@ TALOS_API talos_status talos_ppo_last_loss(talos_ppo* p, float* loss_out) {
   TALOS_REQUIRE(p->steps_in_epoch > 0, TALOS_ERR_ARG, "no optimizer step has run");
   float s[4];
   TALOS_CHECK_CUDA(cudaMemcpyAsync(s, p->step_stats + 4 * ((p->steps_in_epoch - 1) % MAX_STEPS_PER_EPOCH), sizeof(s), cudaMemcpyDeviceToHost, p->ctx->stream));
-  TALOS_CHECK_CUDA(cudaStreamSynchronize(p->ctx->stream));
+  talos_sync_and_check(p->ctx);
   *loss_out = s[2] > 0 ? s[0] / s[2] : 0.f;
   TALOS_ENTRY_END
 }

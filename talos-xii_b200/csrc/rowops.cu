@@ -504,6 +504,8 @@ TALOS_API talos_status talos_softmax_fwd(talos_ctx* ctx, const float* x, float* 
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);
   TALOS_REQUIRE(rows >= 0 && len >= 0 && len <= 1024, TALOS_ERR_SHAPE, "softmax row length must be <= 1024");
+  // a period longer than the row would let row r read columns of row r + 1 (and past the buffer on the last row)
+  TALOS_REQUIRE(causal_period >= 0 && causal_period <= len, TALOS_ERR_SHAPE, "causal_period must be in [0, len]");
   if (rows == 0 || len == 0) return TALOS_OK;       // an empty row sums to 0 (src/simd.rs:335-337)
   TALOS_REQUIRE(x && y, TALOS_ERR_ARG, "null pointer");
   int grid = row_grid(ctx, len <= 128 ? ceil_div(rows, 4) : rows); int npl = (int)ceil_div(len, 32);

@@ -18,6 +18,8 @@ struct TcArgs {
   int chain_kb;                            // CTA-pair 3xTF32 kernel: k-blocks per accumulation chain folded on chip (0: one chain per item)
   int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
   long long stride_c;                      // elements between consecutive batch members of C
+  unsigned wait_spins;                     // poll limit of every bounded wait (WAIT_SPINS unless a test shortened it)
+  int dbg_skip_kb;                         // test hook: CTA 0's producer never loads this k-block of its first item (-1: off)
 };
 
 namespace {
@@ -50,8 +52,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (after raising *abort_flag) when the barrier never flips or when
 // another role has already given up.
+// abort_flag[1] holds the poll limit (set at kernel start from TcArgs::wait_spins); it is read only after the first
+// poll has failed, so the common case costs nothing extra.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t limit = (uint32_t)abort_flag[1];
+  for (uint32_t i = 1; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     // try_wait itself parks the thread for a hardware-defined interval, so the loop is not hot; back off with
     // nanosleep only when the wait is clearly long (the epilogue waiting out a whole main loop, or a stall).

@@ -3,10 +3,11 @@
 //   luck  <seed> <B> <S> <in> <hidden> : LuckTransformer forward on LCG input, loss = mean, backward;
 //                                        writes output, x.grad, then every parameter's grad in parameters() order.
 //   mla   <seed> <B> <S>               : MultiHeadLatentAttention (dim16/h2/r8/rope4/dv8) forward/backward, same layout.
-//   block <dumpB> <B>                  : benchmark config 3 (S64 d256 H8 ff1024, N(0,0.02^2) weights seeds 11-14, x seed 10,
-//                                        upstream gradient seed 15); loss = sum(out*G); writes fp32: out, dx (first dumpB
-//                                        samples each), then the six parameter gradients.
-//   mla4  <dumpB> <B> <token>          : benchmark config 4 (S128 d512 r64 H8 dh64 dr32, seeds 20-27) forward; writes fp32 out.
+//   block <dumpB> <B> 0 [start]        : benchmark config 3 (S64 d256 H8 ff1024, N(0,0.02^2) weights seeds 11-14, x seed 10,
+//                                        upstream gradient seed 15); loss = sum(out*G); writes fp32: out, dx (dumpB samples
+//                                        each, beginning at sample `start`), then the six parameter gradients.
+//   mla4  <dumpB> <B> <token> [start]  : benchmark config 4 (S128 d512 r64 H8 dh64 dr32, seeds 20-27) forward; writes fp32 out
+//                                        of dumpB samples beginning at sample `start`.
 //   rollout <seed> <N> <T> <ctx> [time]: ActorCritic(seed) stepped T times over N simulations through BatchedRollout
 //                                        (KV rings of ctx+1 slots); states N(0, 0.5^2) seed+500 as [T,N,8]; simulation n
 //                                        ends an episode after step t when (t*7 + n*3) % 11 == 0; writes f64 probabilities
@@ -22,8 +23,8 @@
 using namespace talos;
 
 static void dump(std::FILE* f, const std::vector<double>& v) { std::fwrite(v.data(), sizeof(double), v.size(), f); }
-static void dump32(std::FILE* f, const std::vector<double>& v, size_t count) {
-  std::vector<float> t(count); for (size_t i = 0; i < count; ++i) t[i] = (float)v[i]; std::fwrite(t.data(), sizeof(float), count, f);
+static void dump32(std::FILE* f, const std::vector<double>& v, size_t count, size_t first = 0) {
+  std::vector<float> t(count); for (size_t i = 0; i < count; ++i) t[i] = (float)v[first + i]; std::fwrite(t.data(), sizeof(float), count, f);
 }
 static Tensor normal(std::vector<size_t> shape, uint64_t seed, float std_dev) {
   std::vector<float> h(numel(shape)); check(talos_rng_normal_host(seed, 0.f, std_dev, h.data(), (int64_t)h.size()));
@@ -61,21 +62,21 @@ int main(int argc, char** argv) {
       dump(f, out.to_vec()); dump(f, x.grad_vec());
       for (auto& p : m.parameters()) dump(f, p.grad_vec());
     } else if (what == "block") {
-      const size_t dumpB = seed, Bn = B, Sq = 64, D = 256;
+      const size_t dumpB = seed, Bn = B, Sq = 64, D = 256, start = argc > 7 ? std::stoul(argv[7]) : 0;
       TransformerBlock blk(D, 8, 1024, Sq, 1e-6, 0);
       set_normal(blk.w_qkv, 11); set_normal(blk.w_o, 12); set_normal(blk.w_ff1, 13); set_normal(blk.w_ff2, 14);
       Tensor x = normal({Bn, Sq, D}, 10, 1.f), G = normal({Bn, Sq, D}, 15, 1.f);
       Tensor out = blk.forward(x); (out * G).sum().backward();
-      dump32(f, out.to_vec(), dumpB * Sq * D); dump32(f, x.grad_vec(), dumpB * Sq * D);
+      dump32(f, out.to_vec(), dumpB * Sq * D, start * Sq * D); dump32(f, x.grad_vec(), dumpB * Sq * D, start * Sq * D);
       for (auto& p : blk.parameters()) dump32(f, p.grad_vec(), p.len());
     } else if (what == "mla4") {
-      const size_t dumpB = seed, Bn = B, Sq = 128, D = 512;
+      const size_t dumpB = seed, Bn = B, Sq = 128, D = 512, start = argc > 7 ? std::stoul(argv[7]) : 0;
       MultiHeadLatentAttention m(MLAConfig{D, 8, 0, 64, 32, 64, 128}, 0);
       m.token_positions = S != 0;
       set_normal(m.w_dkv, 21); set_normal(m.w_uk, 22); set_normal(m.w_uv, 23); set_normal(m.w_q, 24); set_normal(m.w_kr, 25); set_normal(m.w_qr, 26); set_normal(m.w_o, 27);
       Tensor x = normal({Bn, Sq, D}, 20, 1.f);
       Tensor out = m.forward(x);
-      dump32(f, out.to_vec(), dumpB * Sq * D);
+      dump32(f, out.to_vec(), dumpB * Sq * D, start * Sq * D);
     } else if (what == "rollout") {
       const size_t N = B, T = S, ctx_len = std::stoul(argv[7]);
       const bool timing = argc > 8 && std::string(argv[8]) == "time";
@@ -108,6 +109,8 @@ int main(int argc, char** argv) {
       }
     } else { return 4; }
     std::fclose(f);
+    // a failed tensor-core self-check must fail the run, not hide behind the fp32 stand-in
+    if (Runtime::get().mode != TALOS_MODE_FP32 && talos_ctx_tensor_cores_state(ctx()) < 0) { std::fprintf(stderr, "host_driver: tensor-core self-check failed\n"); return 5; }
   } catch (const std::exception& e) { std::fprintf(stderr, "host_driver: %s\n", e.what()); return 1; }
   return 0;
 }

@@ -19,17 +19,44 @@ def free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return str(p)
 
 
-def launch(kind, world, env=None):
-    port = free_port(); outs = []; procs = []
+def launch(kind, world, env=None, timeout=240):
+    """Runs `world` worker processes and returns their results.  The group is torn down as soon as one rank fails or
+    the time runs out: a rank that exits early would otherwise leave its peers waiting inside a collective, holding
+    their GPUs."""
+    import time
+    port = free_port(); outs = []; procs = []; logs = []
     d = tempfile.mkdtemp()
-    for r in range(world):
-        out = os.path.join(d, "r%d.npz" % r); outs.append(out)
-        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), kind, str(r), str(world), port, out],
-                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=dict(os.environ, **(env or {}))))
-    logs = [p.communicate(timeout=900)[0] for p in procs]
-    for p, log in zip(procs, logs):
-        assert p.returncode == 0, log
-    return [dict(np.load(o)) for o in outs]
+    try:
+        for r in range(world):
+            out = os.path.join(d, "r%d.npz" % r); outs.append(out)
+            log = open(os.path.join(d, "r%d.log" % r), "w+"); logs.append(log)
+            procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dp_worker.py"), kind, str(r), str(world), port, out],
+                                          stdout=log, stderr=subprocess.STDOUT, env=dict(os.environ, **(env or {}))))
+        deadline = time.time() + timeout
+        failed = None
+        while failed is None and any(p.poll() is None for p in procs):
+            if time.time() > deadline:
+                failed = "timed out after %d s" % timeout
+            for r, p in enumerate(procs):
+                if p.poll() not in (None, 0):
+                    failed = "rank %d exited with %d" % (r, p.returncode)
+            time.sleep(0.05)
+        for r, p in enumerate(procs):
+            if failed is None and p.returncode != 0:
+                failed = "rank %d exited with %d" % (r, p.returncode)
+
+        def text(f):
+            f.flush(); f.seek(0); return f.read()
+        assert failed is None, failed + "\n" + "\n".join(text(f)[-4000:] for f in logs)
+        return [dict(np.load(o)) for o in outs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        for p in procs:
+            p.wait()
+        for f in logs:
+            f.close()
 
 
 def single_rank_reference():

@@ -140,6 +140,39 @@ def test_config4_mla_forward_both_position_modes(mode, tol):
         assert np.linalg.norm(full - outs[1]) <= tol * np.linalg.norm(outs[1])
 
 
+@pytest.mark.parametrize("mode,tol", [(1, 1e-5), (2, 2e-3)])
+def test_config3_full_batch_interior_samples_against_the_oracle(mode, tol):
+    # benchmark configuration 3 at its full batch of 1024: samples are independent given the weights, so the oracle
+    # runs 32 samples from the MIDDLE of the batch (rows 500..531 of the same seeded input) and the device's output
+    # and input gradient for exactly those samples must match
+    Bf, Bs, start, S, D, H = 1024, 32, 500, 64, 256, 8
+    P = dict(g1=np.ones(D), g2=np.ones(D), w_qkv=nrm(11, (D, 3 * D), 0.02), w_o=nrm(12, (D, D), 0.02), w_ff1=nrm(13, (D, 1024), 0.02),
+             w_ff2=nrm(14, (1024, D), 0.02))
+    x = nrm(10, (Bf, S, D))[start:start + Bs]; G = nrm(15, (Bf, S, D))[start:start + Bs]
+    y, cache = om.block_fwd(x, P, H, eps=1e-6)
+    dx, _ = om.block_bwd(G, P, cache)
+    flat = run_driver32(["block", mode, Bs, Bf, 0, start])
+    got_y, got_dx = split(flat[:2 * Bs * S * D], [y.shape, dx.shape])
+    assert np.all(np.isfinite(flat))
+    for n, a, b in (("out", got_y, y), ("dx", got_dx, dx)):
+        err = np.linalg.norm(a - b) / np.linalg.norm(b)
+        assert err <= 2 * tol, (n, err)
+
+
+@pytest.mark.parametrize("mode,tol", [(1, 1e-5), (2, 2e-3)])
+def test_config4_full_batch_interior_samples_against_the_oracle(mode, tol):
+    # benchmark configuration 4 at its full batch of 512, token positions: samples 240..271 against the oracle
+    Bf, Bs, start, S, D = 512, 32, 240, 128, 512
+    cfg = om.MLAConfig(D, 8, 64, 32, 64, 128)
+    shapes = dict(dkv=(D, 64), uk=(64, 512), uv=(64, 512), q=(D, 512), kr=(D, 256), qr=(D, 256), o=(512, D))
+    W = {k: nrm(21 + i, shapes[k], 0.02) for i, k in enumerate(["dkv", "uk", "uv", "q", "kr", "qr", "o"])}
+    x = nrm(20, (Bf, S, D))[start:start + Bs]
+    ref = om.mla_forward(x, W, cfg, "token")
+    got = run_driver32(["mla4", mode, Bs, Bf, 1, start]).reshape(ref.shape)
+    err = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert err <= tol, err
+
+
 @pytest.mark.parametrize("mode,tol", [(0, 1e-5), (1, 1e-5), (2, 2e-3)])
 def test_batched_rollout_matches_per_simulation_cached_inference(mode, tol):
     # ActorCritic::step_inference_cached (src/ppo.rs:391-432) + prune_cache (src/sim.rs:171-175) per simulation in the

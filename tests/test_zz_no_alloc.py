@@ -17,13 +17,18 @@ def test_colsum_noalloc_matches_colsum_on_consecutive_calls(talos):
     gen = torch.Generator(device="cuda").manual_seed(1234)
     # second shape is smaller in both directions, so stale partial sums of the first call sit right next
     # to (and beyond) the region the second call uses
-    for rows, n, acc in [(70000, 256, 0), (777, 33, 1), (5, 1024, 0), (65536, 32, 1)]:
+    for i, (rows, n, acc) in enumerate([(70000, 256, 0), (777, 33, 1), (5, 1024, 0), (65536, 32, 1)]):
         g = torch.randn(rows, n, device="cuda", generator=gen)
         start = torch.randn(n, device="cuda", generator=gen)
         want = start.clone(); got = start.clone()
         talos.lib.talos_colsum(ctx.handle, talos.ptr(g), talos.ptr(want), rows, n, acc)
+        ctx.synchronize()
+        # Creating the context resolved the scratch array's address (and made the driver set the array aside), so not
+        # even the first call may change the amount of free device memory.
+        free_before = torch.cuda.mem_get_info(0)[0]
         talos.lib.talos_colsum_noalloc(ctx.handle, talos.ptr(g), talos.ptr(got), rows, n, acc)
         ctx.synchronize()
+        assert torch.cuda.mem_get_info(0)[0] == free_before, "call %d changed the free device memory" % i
         ref = g.double().sum(0) + (start.double() if acc else 0)
         scale = float(ref.abs().max())
         assert float((got.double() - want.double()).abs().max()) <= 1e-5 * scale, (rows, n)
