@@ -63,10 +63,10 @@ def build_host_tests():
     root = os.path.dirname(HERE)
     src_dir = os.path.join(root, "tests", "cpp"); out_dir = os.path.join(src_dir, "bin")
     os.makedirs(out_dir, exist_ok=True)
-    hdr = os.path.join(HERE, "host", "talos.hpp")
+    hdr_time = max(os.path.getmtime(os.path.join(HERE, "host", h)) for h in os.listdir(os.path.join(HERE, "host")))
     for name in ("test_reference_kats", "host_driver"):
         src = os.path.join(src_dir, name + ".cpp"); out = os.path.join(out_dir, name)
-        if os.path.exists(out) and os.path.getmtime(out) > max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(LIB)):
+        if os.path.exists(out) and os.path.getmtime(out) > max(os.path.getmtime(src), hdr_time, os.path.getmtime(LIB)):
             continue
         cmd = ["g++", "-std=c++17", "-O2", "-Wall", "-o", out, src, "-L", HERE, "-ltalos_b200", "-Wl,-rpath," + HERE, "-Wl,-rpath,$ORIGIN/../../../talos-xii_b200"]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)

@@ -242,24 +242,41 @@ void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* act
   const int64_t mb = p->cfg.minibatch;
   int32_t done = 0;
   std::vector<float> stats;
+  const int64_t steps_per_epoch = (N + mb - 1) / mb;
+  TALOS_REQUIRE(steps_per_epoch <= MAX_STEPS_PER_EPOCH, TALOS_ERR_UNSUPPORTED, "too many minibatches per epoch");
+  // With the early stop disabled nothing on the host depends on an epoch's KL before the next epoch starts, so the
+  // per-step statistics of ALL epochs are read back once at the end and the stream never drains in between (each drain
+  // costs the launch queue's refill, tens of microseconds).  With the stop enabled (the reference's behaviour,
+  // src/ppo.rs:762-767) every epoch ends with the read-back it needs.
+  const bool defer = !(kl_stop > 0.f) && (int64_t)epochs * steps_per_epoch <= MAX_STEPS_PER_EPOCH;
+  auto epoch_mean_kl = [&](const float* st, int64_t steps) {
+    double kl = 0, cnt = 0;
+    for (int64_t i = 0; i < steps; ++i) { kl += st[4 * i + 1]; cnt += st[4 * i + 2]; }
+    return cnt > 0 ? (float)(kl / cnt) : 0.f;
+  };
+  p->steps_in_epoch = 0;
   for (int32_t e = 0; e < epochs; ++e) {
-    p->steps_in_epoch = 0;
+    if (!defer) p->steps_in_epoch = 0;                       // (deferred: the slots of later epochs follow the earlier ones)
     for (int64_t s = 0; s < N; s += mb) {
       int64_t n = std::min(mb, N - s);
       if (ready && e == 0) TALOS_CHECK_CUDA(cudaStreamWaitEvent(p->ctx->stream, (*ready)[(size_t)(s / mb)], 0));
       step(p, comm, obs + s * p->cfg.obs_dim, actions + s, old_logp + s, adv + s, ret + s, n);
-      TALOS_REQUIRE(p->steps_in_epoch <= MAX_STEPS_PER_EPOCH, TALOS_ERR_UNSUPPORTED, "too many minibatches per epoch");
     }
     done = e + 1;
+    if (defer) continue;
     // mean approx-KL of the epoch (src/ppo.rs:729-731, :762-767): the step's device->host read
     stats.resize(4 * (size_t)p->steps_in_epoch);
     TALOS_CHECK_CUDA(cudaMemcpyAsync(stats.data(), p->step_stats, stats.size() * sizeof(float), cudaMemcpyDeviceToHost, p->ctx->stream));
     talos_sync_and_check(p->ctx);        // a kernel that gave up (or met a bad action) ends the update here: no further epochs on garbage gradients
-    double kl = 0, cnt = 0;
-    for (int64_t i = 0; i < p->steps_in_epoch; ++i) { kl += stats[4 * i + 1]; cnt += stats[4 * i + 2]; }
-    float mean_kl = cnt > 0 ? (float)(kl / cnt) : 0.f;
+    const float mean_kl = epoch_mean_kl(stats.data(), p->steps_in_epoch);
     if (epoch_kl) epoch_kl[e] = mean_kl;
     if (kl_stop > 0.f && mean_kl > kl_stop * 1.5f) break;
+  }
+  if (defer) {
+    stats.resize(4 * (size_t)p->steps_in_epoch);
+    TALOS_CHECK_CUDA(cudaMemcpyAsync(stats.data(), p->step_stats, stats.size() * sizeof(float), cudaMemcpyDeviceToHost, p->ctx->stream));
+    talos_sync_and_check(p->ctx);
+    for (int32_t e = 0; e < done; ++e) if (epoch_kl) epoch_kl[e] = epoch_mean_kl(stats.data() + 4 * (size_t)(e * steps_per_epoch), steps_per_epoch);
   }
   if (epochs_run) *epochs_run = done;
 }

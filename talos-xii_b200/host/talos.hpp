@@ -268,8 +268,12 @@ struct Module {                                                                 
 
 inline size_t rows_of(const Tensor& x, size_t last) { TALOS_ASSERT(!x.shape.empty() && x.shape.back() == last, "MatMul dimension mismatch"); return x.len() / last; }
 
+// Tag for constructing a layer whose fields a deserialiser fills in afterwards (no random initialisation, no upload).
+struct Uninit {};
+
 struct Linear : Module {                                                            // src/nn.rs:12-142
   Tensor weight; std::optional<Tensor> bias; size_t in_features, out_features;
+  explicit Linear(Uninit) : in_features(0), out_features(0) {}
   Linear(size_t in_f, size_t out_f, bool with_bias, uint64_t seed) : in_features(in_f), out_features(out_f) {
     const double limit = std::sqrt(6.0 / (double)(in_f + out_f));                   // Xavier (:22)
     weight = Tensor::rand({in_f, out_f}, -limit, limit, seed);
@@ -304,6 +308,7 @@ struct Linear : Module {                                                        
 
 struct RMSNorm : Module {                                                           // src/nn.rs:145-304
   Tensor weight; double eps; size_t dim;
+  explicit RMSNorm(Uninit) : eps(0.0), dim(0) {}
   RMSNorm(size_t d, double e, uint64_t /*seed*/) : eps(e), dim(d) { weight = Tensor::new_(std::vector<double>(d, 1.0), {d}); }
   Tensor forward(const Tensor& x) const override {
     TALOS_ASSERT(!x.shape.empty() && x.shape.back() == dim, "RMSNorm dim mismatch");
@@ -325,6 +330,7 @@ struct RMSNorm : Module {                                                       
 
 struct RoPE {                                                                       // src/transformer.rs:220-371
   size_t dim; double base = 10000.0; size_t max_len; Buf cos_cache, sin_cache;
+  explicit RoPE(Uninit) : dim(0), max_len(0) {}
   RoPE(size_t d, size_t max_l) : dim(d), max_len(max_l) {
     cos_cache = make_buf(max_l * d / 2, false); sin_cache = make_buf(max_l * d / 2, false);
     check(talos_rope_table(ctx(), (int64_t)d, (int64_t)max_l, base, cos_cache->dev, sin_cache->dev));
@@ -367,6 +373,7 @@ struct KVCache {                                                                
 struct MultiHeadLatentAttention {                                                   // :375-1184
   MLAConfig config; Linear w_dkv, w_uk, w_uv, w_q, w_kr, w_qr, w_o; RoPE rope;
   bool token_positions = false;      // false: the crate's autograd-path behaviour (rotation by head index)
+  explicit MultiHeadLatentAttention(Uninit u) : config{}, w_dkv(u), w_uk(u), w_uv(u), w_q(u), w_kr(u), w_qr(u), w_o(u), rope(u) {}
   MultiHeadLatentAttention(const MLAConfig& c, uint64_t seed)
       : config(c), w_dkv(c.dim, c.kv_lora_rank, false, seed), w_uk(c.kv_lora_rank, c.num_heads * c.v_head_dim, false, seed + 1),
         w_uv(c.kv_lora_rank, c.num_heads * c.v_head_dim, false, seed + 2), w_q(c.dim, c.num_heads * c.v_head_dim, false, seed + 3),
@@ -386,8 +393,7 @@ struct MultiHeadLatentAttention {                                               
       else check(talos_copy_device(ctx(), cat->dev, a.d(), sizeof(float) * a.len()));
       int64_t shp[4] = {(int64_t)B, (int64_t)S, (int64_t)H, (int64_t)(wa + wb)};
       check(talos_transpose(ctx(), cat->dev, dst, shp, 4, 1, 2, 0));
-      Runtime::get().synchronize();                                                 // `cat` is released at scope exit
-    };
+    };                                                                              // `cat` goes back to the ctx allocator, which hands it only to LATER work on the stream
     pack(qc, &qr, dh, dr, q->dev); pack(kc, &kr, dh, dr, k->dev); pack(v, nullptr, dh, 0, vv->dev);
     Tensor out = Tensor::result({B, S, H * dh}, {qc, qr, kc, kr, v}, [=](const Tensor& o, const std::vector<Tensor>& p) {
       Buf go = make_buf(BH * S * dh, false), gq = make_buf(BH * S * tot, false), gk = make_buf(BH * S * tot, false), gv = make_buf(BH * S * dh, false);
@@ -399,7 +405,6 @@ struct MultiHeadLatentAttention {                                               
         int64_t bhsw[4] = {(int64_t)B, (int64_t)H, (int64_t)S, (int64_t)w};
         check(talos_transpose(ctx(), src, t->dev, bhsw, 4, 1, 2, 0));
         check(talos_split_last(ctx(), t->dev, ga, gb, (int64_t)(B * S * H), (int64_t)wa, (int64_t)wb, 1));
-        Runtime::get().synchronize();
       };
       unpack(gq->dev, tot, p[0].g(), p[1].g(), dh, dr); unpack(gk->dev, tot, p[2].g(), p[3].g(), dh, dr); unpack(gv->dev, dh, p[4].g(), nullptr, dh, 0);
     });
@@ -407,7 +412,6 @@ struct MultiHeadLatentAttention {                                               
     check(talos_attention_fwd(ctx(), q->dev, k->dev, vv->dev, att->dev, probs->dev, (int64_t)BH, (int64_t)S, (int64_t)tot, (int64_t)dh, scale, causal ? 1 : 0, mode()));
     int64_t bhsd[4] = {(int64_t)B, (int64_t)H, (int64_t)S, (int64_t)dh};
     check(talos_transpose(ctx(), att->dev, out.d(), bhsd, 4, 1, 2, 0));
-    Runtime::get().synchronize();
     return out;
   }
   Tensor forward(const Tensor& x) const {                                           // :478-560
@@ -441,7 +445,7 @@ struct MultiHeadLatentAttention {                                               
         check(talos_copy_device(ctx(), nk->dev + h * ncap * tot, cache.k->dev + h * cache.cap * tot, sizeof(float) * cache.len * tot));
         check(talos_copy_device(ctx(), nv->dev + h * ncap * dh, cache.v->dev + h * cache.cap * dh, sizeof(float) * cache.len * dh));
       }
-      Runtime::get().synchronize(); cache.k = nk; cache.v = nv; cache.cap = ncap; cache.k_width = tot; cache.v_width = dh;
+      cache.k = nk; cache.v = nv; cache.cap = ncap; cache.k_width = tot; cache.v_width = dh;
     }
     for (size_t t = 0; t < S; ++t) for (size_t h = 0; h < H; ++h) {
       check(talos_copy_device(ctx(), cache.k->dev + (h * cache.cap + cache.len + t) * tot, k.d() + (t * H + h) * tot, sizeof(float) * tot));
@@ -467,12 +471,13 @@ struct MultiHeadLatentAttention {                                               
       check(talos_copy_device(ctx(), nk->dev + h * cache.cap * tot, cache.k->dev + (h * cache.cap + rm) * tot, sizeof(float) * max_seq_len * tot));
       check(talos_copy_device(ctx(), nv->dev + h * cache.cap * dh, cache.v->dev + (h * cache.cap + rm) * dh, sizeof(float) * max_seq_len * dh));
     }
-    Runtime::get().synchronize(); cache.k = nk; cache.v = nv; cache.len = max_seq_len;
+    cache.k = nk; cache.v = nv; cache.len = max_seq_len;
   }
 };
 
 struct LuckTransformer : Module {                                                   // src/transformer.rs:36-216
   Linear embed; RMSNorm norm_1; MultiHeadLatentAttention mla_layer; RMSNorm norm_2; Linear ffn_1, ffn_2; RMSNorm norm_final; Linear out_proj;
+  explicit LuckTransformer(Uninit u) : embed(u), norm_1(u), mla_layer(u), norm_2(u), ffn_1(u), ffn_2(u), norm_final(u), out_proj(u) {}
   LuckTransformer(size_t in_dim, size_t hidden, bool /*bias*/, uint64_t seed)
       : embed(in_dim, hidden, true, seed), norm_1(hidden, 1e-5, seed + 5), mla_layer(MLAConfig{hidden, 4, 0, 32, 16, hidden / 4, 256}, seed + 10),
         norm_2(hidden, 1e-5, seed + 15), ffn_1(hidden, hidden * 2, true, seed + 20), ffn_2(hidden * 2, hidden, true, seed + 30),
@@ -554,6 +559,7 @@ struct TransformerBlock : Module {
 struct ActorCritic {                                                                // src/ppo.rs:247-307
   static constexpr size_t DIM = 8, ACTION_SPACE = 5;                                // src/neural.rs:3, src/ppo.rs:15
   LuckTransformer backbone; Linear actor_head, critic_head;
+  explicit ActorCritic(Uninit u) : backbone(u), actor_head(u), critic_head(u) {}
   explicit ActorCritic(uint64_t seed) : backbone(DIM, 64, true, seed), actor_head(64, ACTION_SPACE, true, seed + 100), critic_head(64, 1, true, seed + 200) {}
   Tensor head(const Tensor& state, const Linear& h) const {
     Tensor x = state.shape.size() == 1 ? state.reshape({1, 1, state.shape[0]}) : state.shape.size() == 2 ? state.reshape({1, state.shape[0], state.shape[1]}) : state;
@@ -618,11 +624,9 @@ inline Tensor dqn_loss(const Tensor& q, const std::vector<int32_t>& actions, con
     check(talos_fill_from_scalar(ctx(), o.g(), 1.f, scaled->dev, (int64_t)(B * A), 0));
     check(talos_eltwise_binary(ctx(), TALOS_EW_MUL, scaled->dev, dq->dev, scaled->dev, (int64_t)(B * A)));
     check(talos_eltwise_binary(ctx(), TALOS_EW_ADD, p[0].g(), scaled->dev, p[0].g(), (int64_t)(B * A)));
-    Runtime::get().synchronize();
   });
   check(talos_dqn_loss_fwd_bwd(ctx(), q.d(), (const int32_t*)act->dev, target.d(), loss.d(), dq->dev, (int64_t)B, (int64_t)A));
-  Runtime::get().synchronize();                                                     // `act`, r, d are released at scope exit
-  return loss;
+  return loss;                                                                      // `act`, r, d go back to the stream-ordered allocator
 }
 
 // RunningMeanStd (src/ppo.rs:444-480): host arithmetic in f64 exactly as the crate (a few scalars per reward).
@@ -649,7 +653,6 @@ inline std::pair<Tensor, Tensor> gae_advantages(const Tensor& rewards, const Ten
   check(talos_gae(ctx(), rewards.d(), values.d(), (const int32_t*)term->dev, (int64_t)len, (float)gamma, (float)lambda, (float)reward_normalizer.mean,
                   (float)reward_normalizer.var, adv.d(), ret.d()));
   check(talos_normalize_slice(ctx(), adv.d(), (int64_t)len, adv.d(), nullptr));
-  Runtime::get().synchronize();                                                   // `term` is released at scope exit
   return {adv, ret};
 }
 

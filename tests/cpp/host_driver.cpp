@@ -8,6 +8,10 @@
 //                                        each, beginning at sample `start`), then the six parameter gradients.
 //   mla4  <dumpB> <B> <token> [start]  : benchmark config 4 (S128 d512 r64 H8 dh64 dr32, seeds 20-27) forward; writes fp32 out
 //                                        of dumpB samples beginning at sample `start`.
+//   serde <seed> <B> <S> <prefix>      : ActorCritic(seed) written with save_ppo_model to <prefix>.bin (bincode) and <prefix>
+//                                        (JSON), read back from each and through load_ppo_model (binary first; JSON when
+//                                        only <prefix>.json_only exists); writes f64 actor logits on LCG states [B,S,8] of the
+//                                        original and of the four loaded models, [5][B,5].
 //   rollout <seed> <N> <T> <ctx> [time]: ActorCritic(seed) stepped T times over N simulations through BatchedRollout
 //                                        (KV rings of ctx+1 slots); states N(0, 0.5^2) seed+500 as [T,N,8]; simulation n
 //                                        ends an episode after step t when (t*7 + n*3) % 11 == 0; writes f64 probabilities
@@ -19,7 +23,7 @@
 #include <string>
 #include <vector>
 
-#include "../../talos-xii_b200/host/talos.hpp"
+#include "../../talos-xii_b200/host/talos_serde.hpp"
 using namespace talos;
 
 static void dump(std::FILE* f, const std::vector<double>& v) { std::fwrite(v.data(), sizeof(double), v.size(), f); }
@@ -77,6 +81,22 @@ int main(int argc, char** argv) {
       Tensor x = normal({Bn, Sq, D}, 20, 1.f);
       Tensor out = m.forward(x);
       dump32(f, out.to_vec(), dumpB * Sq * D, start * Sq * D);
+    } else if (what == "serde") {
+      const std::string prefix = argv[7];
+      ActorCritic ac(seed);
+      if (!serde::save_ppo_model(ac, prefix)) { std::fprintf(stderr, "host_driver: cannot write %s\n", prefix.c_str()); return 6; }
+      std::string raw, js;
+      if (!serde::read_file(prefix + ".bin", &raw) || !serde::read_file(prefix, &js)) return 6;
+      ActorCritic from_bin = serde::actor_critic_from_bincode(std::vector<uint8_t>(raw.begin(), raw.end()));
+      ActorCritic from_json = serde::actor_critic_from_json(js);
+      std::optional<ActorCritic> loaded = serde::load_ppo_model(prefix);                       // finds the binary file
+      if (!serde::write_file(prefix + ".json_only", js.data(), js.size())) return 6;
+      std::optional<ActorCritic> loaded_json = serde::load_ppo_model(prefix + ".json_only");  // no .bin beside it: JSON
+      if (!loaded || !loaded_json || serde::load_ppo_model(prefix + ".missing")) { std::fprintf(stderr, "host_driver: load_ppo_model\n"); return 7; }
+      Tensor x = Tensor::rand({B, S, ActorCritic::DIM}, -0.5, 0.5, seed + 1000);
+      for (const ActorCritic* m : {&ac, &from_bin, &from_json, &*loaded, &*loaded_json}) dump(f, m->forward_actor(x).to_vec());
+      // a second save of a loaded model must reproduce the files byte for byte
+      if (serde::to_bincode(from_json) != std::vector<uint8_t>(raw.begin(), raw.end()) || serde::to_json(from_bin) != js) { std::fprintf(stderr, "host_driver: re-serialised model differs\n"); return 8; }
     } else if (what == "rollout") {
       const size_t N = B, T = S, ctx_len = std::stoul(argv[7]);
       const bool timing = argc > 8 && std::string(argv[8]) == "time";

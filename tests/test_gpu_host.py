@@ -29,7 +29,7 @@ def run_driver32(args):
         return np.fromfile(f.name, dtype=np.float32).astype(np.float64)
 
 
-def run_driver(args, symmetric=True):
+def run_driver(args, symmetric=True):  # (args after the first two go behind the output file name)
     env = dict(os.environ)
     if symmetric: env["TALOS_SYMMETRIC_WEIGHTS"] = "1"
     with tempfile.NamedTemporaryFile(suffix=".bin") as f:
@@ -208,3 +208,108 @@ def test_batched_rollout_with_the_crates_own_weights():
     resets = np.array([[1 if (t * 7 + n * 3) % 11 == 0 else 0 for n in range(N)] for t in range(T)])
     ref = om.rollout_reference(om.ActorCritic(seed), states, resets, ctx_len)
     assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 1e-5
+
+
+def _ryu_like(x):
+    """An f64 as serde_json writes it: shortest round-trip digits in the layout of the `ryu` crate (see
+    talos-xii_b200/host/talos_serde.hpp), written independently here from Python's own shortest-digits repr."""
+    import math
+    if not math.isfinite(x):
+        return "null"
+    if x == 0.0:
+        return "-0.0" if math.copysign(1.0, x) < 0 else "0.0"
+    sign = "-" if x < 0 else ""
+    m, e = ("%r" % abs(x)).lower(), 0
+    if "e" in m:
+        m, ee = m.split("e"); e = int(ee)
+    ip, _, fp = m.partition(".")
+    digits = (ip + fp).lstrip("0"); kk = len(ip.lstrip("0")) + e if ip.strip("0") else e - (len(fp) - len(fp.lstrip("0")))
+    digits = digits.rstrip("0") or "0"; n = len(digits)
+    if n <= kk <= 16:
+        return sign + digits + "0" * (kk - n) + ".0"
+    if 0 < kk <= 16:
+        return sign + digits[:kk] + "." + digits[kk:]
+    if -5 < kk <= 0:
+        return sign + "0." + "0" * (-kk) + digits
+    return sign + digits[0] + ("." + digits[1:] if n > 1 else "") + "e" + str(kk - 1)
+
+
+def test_ryu_like_formatter_known_cases():
+    # (the fixed-point form reaches down to four zeros after the point: 1e-5 is 0.00001, 1e-6 is 1e-6)
+    cases = {1.0: "1.0", 10000.0: "10000.0", 1e-5: "0.00001", 1e-6: "1e-6", 0.001: "0.001", 1.2345e-7: "1.2345e-7", 1e16: "1e16", 1e15: "1000000000000000.0",
+             -0.5: "-0.5", 123456.789: "123456.789", 1e21: "1e21", 0.00001234: "0.00001234", 1.234e-6: "1.234e-6", 1234000.0: "1234000.0",
+             float(np.float32(0.1)): "0.10000000149011612"}
+    for v, want in cases.items():
+        assert _ryu_like(v) == want, (v, _ryu_like(v), want)
+
+
+def test_model_files_have_the_crates_byte_layout_and_round_trip(tmp_path):
+    # save_ppo_model / load_ppo_model (src/main.rs:123-166): the files the host mirror writes are compared, byte for
+    # byte, with files assembled here by hand from the bincode 1.x / serde_json rules and the oracle's copy of the
+    # LCG-initialised weights; the models read back from them must compute exactly what the original computes.
+    import math
+    import struct
+    seed, B, S = 12345, 2, 3
+    prefix = str(tmp_path / "ppo.cache")
+    flat = run_driver(["serde", 0, seed, B, S, prefix], symmetric=False)
+    outs = flat.reshape(5, -1)
+    for i in range(1, 5):
+        assert np.array_equal(outs[0], outs[i]), i
+    ac = om.ActorCritic(seed)
+    bb = ac.backbone; cfg = bb.cfg
+    f32 = lambda a: np.asarray(a, dtype=np.float64).astype(np.float32).astype(np.float64)
+    u64 = lambda v: struct.pack("<Q", v)
+
+    def tensor(a, shape):
+        a = f32(a).ravel()
+        return u64(a.size) + a.astype("<f8").tobytes() + u64(len(shape)) + b"".join(u64(d) for d in shape)
+
+    def linear(W, b):
+        fi, fo = W.shape
+        return tensor(W, (fi, fo)) + (b"\x01" + tensor(b, (fo,)) if b is not None else b"\x00") + u64(fi) + u64(fo)
+
+    def rmsnorm(g, eps):
+        return tensor(g, (g.size,)) + struct.pack("<d", eps) + u64(g.size)
+    cos_t, sin_t = [], []
+    dr = cfg.qk_rope_dim
+    for pos in range(cfg.max_seq_len):
+        for i in range(dr // 2):
+            theta = 1.0 / math.pow(10000.0, (2 * i) / dr); ang = pos * theta
+            cos_t.append(math.cos(ang)); sin_t.append(math.sin(ang))
+    vec = lambda v: u64(len(v)) + np.asarray(v, dtype="<f8").tobytes()
+    mla = b"".join(u64(v) for v in (cfg.dim, cfg.num_heads, 0, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.v_head_dim, cfg.max_seq_len))
+    mla += b"".join(linear(bb.mla[k], None) for k in ("dkv", "uk", "uv", "q", "kr", "qr", "o"))
+    mla += u64(dr) + struct.pack("<d", 10000.0) + vec(cos_t) + vec(sin_t)
+    want = (linear(*bb.embed) + rmsnorm(bb.g1, 1e-5) + mla + rmsnorm(bb.g2, 1e-5) + linear(*bb.ffn_1) + linear(*bb.ffn_2) + rmsnorm(bb.gf, 1e-5)
+            + linear(*bb.out_proj) + linear(*ac.actor) + linear(*ac.critic))
+    got = open(prefix + ".bin", "rb").read()
+    assert len(got) == len(want) and got == want
+
+    # JSON: same content, keys in declaration order, numbers in serde_json's spelling
+    num = _ryu_like
+    arr = lambda v: "[" + ",".join(num(float(x)) for x in v) + "]"
+    jt = lambda a, shape: '{"data":%s,"shape":[%s]}' % (arr(f32(a).ravel()), ",".join(str(d) for d in shape))
+    jl = lambda W, b: '{"weight":%s,"bias":%s,"in_features":%d,"out_features":%d}' % (jt(W, W.shape), jt(b, (W.shape[1],)) if b is not None else "null", W.shape[0], W.shape[1])
+    jn = lambda g, eps: '{"weight":%s,"eps":%s,"dim":%d}' % (jt(g, (g.size,)), num(eps), g.size)
+    jc = '{"dim":%d,"num_heads":%d,"q_lora_rank":0,"kv_lora_rank":%d,"qk_rope_dim":%d,"v_head_dim":%d,"max_seq_len":%d}' % (
+        cfg.dim, cfg.num_heads, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.v_head_dim, cfg.max_seq_len)
+    jm = '{"config":%s,%s,"rope":{"dim":%d,"base":10000.0,"cos_cache":%s,"sin_cache":%s}}' % (
+        jc, ",".join('"w_%s":%s' % (k, jl(bb.mla[k], None)) for k in ("dkv", "uk", "uv", "q", "kr", "qr", "o")), dr, arr(cos_t), arr(sin_t))
+    jb = '{"embed":%s,"norm_1":%s,"mla_layer":%s,"norm_2":%s,"ffn_1":%s,"ffn_2":%s,"norm_final":%s,"out_proj":%s}' % (
+        jl(*bb.embed), jn(bb.g1, 1e-5), jm, jn(bb.g2, 1e-5), jl(*bb.ffn_1), jl(*bb.ffn_2), jn(bb.gf, 1e-5), jl(*bb.out_proj))
+    want_js = '{"backbone":%s,"actor_head":%s,"critic_head":%s}' % (jb, jl(*ac.actor), jl(*ac.critic))
+    got_js = open(prefix).read()
+    assert got_js == want_js
+    import json
+    parsed = json.loads(got_js)                                    # and it is JSON: key order as the structs declare their fields
+    assert list(parsed) == ["backbone", "actor_head", "critic_head"]
+    assert list(parsed["backbone"]) == ["embed", "norm_1", "mla_layer", "norm_2", "ffn_1", "ffn_2", "norm_final", "out_proj"]
+    assert list(parsed["backbone"]["mla_layer"]) == ["config", "w_dkv", "w_uk", "w_uv", "w_q", "w_kr", "w_qr", "w_o", "rope"]
+    # the loaded models agree with the oracle's forward on the same LCG states
+    x = orc.f32r(orc.lcg_rand((B, S, 8), -0.5, 0.5, seed + 1000))
+    for name in ("embed", "ffn_1", "ffn_2", "out_proj"):
+        W, b = getattr(bb, name); setattr(bb, name, (f32(W), b))
+    bb.mla = {k: f32(v) for k, v in bb.mla.items()}
+    ac.actor = (f32(ac.actor[0]), ac.actor[1])
+    ref = np.stack([ac.forward_actor(x[i:i + 1]) for i in range(B)]).ravel()
+    assert np.linalg.norm(outs[0] - ref) <= 2e-5 * np.linalg.norm(ref)

@@ -122,12 +122,13 @@ def test_simd_slice_primitives(talos, ctx):
     import torch
     # the reference's own known-answer tests (src/dbn.rs:391-415) ...
     row = np.array([1.0, 2.5, -3.0, 4.0, -5.5, 6.25, 7.75, -8.0]); out = torch.zeros(8, device="cuda:0")
-    talos.lib.talos_axpy(ctx.handle, talos.ptr(out), talos.ptr(dev(row)), 0.75, 8); ctx.synchronize()
+    d_row = dev(row)
+    talos.lib.talos_axpy(ctx.handle, talos.ptr(out), talos.ptr(d_row), 0.75, 8); ctx.synchronize()
     assert np.abs(host(out) - 0.75 * row).max() < 1e-9 * 8                 # values are exact in fp32
     a = np.array([1.5, -2.0, 3.25, 4.0, -5.0, 6.5, -7.25, 8.0]); b = np.array([0.5, 1.25, -2.0, 3.0, 4.5, -5.5, 6.0, -7.0])
-    d = torch.zeros(1, device="cuda:0")
-    talos.lib.talos_dot(ctx.handle, talos.ptr(dev(a)), talos.ptr(dev(b)), 8, talos.ptr(d), 0); ctx.synchronize()
-    assert abs(float(d) - float(np.dot(a, b))) < 1e-9 * 200                # -154.625, exact in fp32
+    d = torch.zeros(1, device="cuda:0"); d_a, d_b = dev(a), dev(b)      # (named: a temporary would be freed, and its memory reused, before the call)
+    talos.lib.talos_dot(ctx.handle, talos.ptr(d_a), talos.ptr(d_b), 8, talos.ptr(d), 0); ctx.synchronize()
+    assert abs(float(d) - float(np.dot(a, b))) < 1e-9 * 200                # -154.0, exact in fp32
     # ... and against the oracle's restatement at lengths around the vector width, unaligned starts, large n
     for n, off in [(1, 0), (3, 1), (4, 0), (1000, 0), (1001, 3), (1 << 20, 0), ((1 << 20) + 5, 1)]:
         X = normal(n, (n + off,)); Y = normal(n + 1, (n + off,)); Z = normal(n + 2, (n + off,))
@@ -159,7 +160,8 @@ def test_softmax_rejects_a_causal_period_longer_than_the_row(talos, ctx):
     rows = n = 100
     X = normal(9, (rows, n), 2.0); scale = 1.0 / math.sqrt(7.0)
     y = torch.empty(rows, n, device="cuda:0")
-    talos.lib.talos_softmax_fwd(ctx.handle, talos.ptr(dev(X)), talos.ptr(y), rows, n, scale, n); ctx.synchronize()
+    d_x = dev(X)
+    talos.lib.talos_softmax_fwd(ctx.handle, talos.ptr(d_x), talos.ptr(y), rows, n, scale, n); ctx.synchronize()
     assert rel_err(y, orc.softmax(orc.f32r(X) * np.float64(np.float32(scale)), n)) <= 2e-6
 
 
