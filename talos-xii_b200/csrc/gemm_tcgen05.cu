@@ -94,7 +94,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       auto pf_decode = [&]() {
         if (pf_it >= items) return;
         pf_bz = pf_it / per_batch; const int r = pf_it - pf_bz * per_batch;
-        const int ks = r / tiles_mn, rem = r % tiles_mn; pf_nb = rem / g.m_tiles; pf_mb = rem % g.m_tiles;
+        const int ks = r / tiles_mn, rem = r % tiles_mn; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, pf_mb, pf_nb);
         pf_kb = ks * g.kb_per_split; pf_kb1 = min(g.kb_total, pf_kb + g.kb_per_split);
       };
       auto pf_step = [&]() {                                   // prefetch the k-block at the look-ahead position, then advance it
@@ -110,10 +110,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (++pf_kb >= pf_kb1) { pf_it += gridDim.x; pf_decode(); }
       };
       const bool pf_on = g.pf_a || g.pf_b;
+      const bool b_resident = BPS && g.kb_total == 1 && g.n_tiles == 1 && g.batch == 1 && g.splits == 1;
+      int issued = 0;
       if (pf_on) { pf_decode(); for (int i = 0; i < PF_DIST; ++i) pf_step(); }
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
         const int bz = it / per_batch, r = it - bz * per_batch;
-        const int ks = r / tiles_mn, rem = r % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+        const int ks = r / tiles_mn, rem = r % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (pf_on) pf_step();
@@ -121,17 +123,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // Test hook: this stage is never armed nor loaded, so its consumers' bounded waits run out and the CTA
           // leaves through the abort path (nothing faults; the loads already in flight land and are ignored).
           if (g.dbg_skip_kb >= 0 && blockIdx.x == 0 && it == 0 && kb - kb0 == g.dbg_skip_kb) { if (++stage == STAGES) { stage = 0; phase ^= 1; } continue; }
-          mbar_expect_tx(full + stage, A_BYTES + B_BYTES + (BPS ? B_BYTES : 0));
+          // A one-k-block product with a single column panel (the K = 32 input gradient of the fused heads) uses the
+          // SAME B tile for every output tile: each stage's B buffers are filled on the stage's first use and kept.
+          const bool load_b = !b_resident || issued < STAGES;
+          ++issued;
+          mbar_expect_tx(full + stage, A_BYTES + (load_b ? B_BYTES + (BPS ? B_BYTES : 0) : 0));
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
-          if (BPS) {
+          if (BPS && load_b) {
             uint8_t* bl_dst = sBlo + stage * B_BYTES;
             if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_3d(bl_dst + j * (BK * 128), &tmap_b_lo, nb * BN + 32 * j, kb * BK, bz, full + stage); }
             else tma_load_3d(bl_dst, &tmap_b_lo, kb * BK, nb * BN, bz, full + stage);
           }
           if (A_MN) { for (int j = 0; j < BM / 32; ++j) tma_load_3d(a_dst + j * (BK * 128), &tmap_a, mb * BM + 32 * j, kb * BK, bz, full + stage); }
           else tma_load_3d(a_dst, &tmap_a, kb * BK, mb * BM, bz, full + stage);
-          if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_3d(b_dst + j * (BK * 128), &tmap_b, nb * BN + 32 * j, kb * BK, bz, full + stage); }
-          else tma_load_3d(b_dst, &tmap_b, kb * BK, nb * BN, bz, full + stage);
+          if (load_b) {
+            if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_3d(b_dst + j * (BK * 128), &tmap_b, nb * BN + 32 * j, kb * BK, bz, full + stage); }
+            else tma_load_3d(b_dst, &tmap_b, kb * BK, nb * BN, bz, full + stage);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -183,7 +191,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int bz = it / per_batch, r = it - bz * per_batch;
-      const int ks = r / tiles_mn, rem = r % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+      const int ks = r / tiles_mn, rem = r % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
       if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
       tc_fence_after();
       tc_epilogue_tile<BN, EPI_WARPS>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32), (long long)mb * BM, nb, ks, bz, store_count);
@@ -364,6 +372,9 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   const bool pair_shape = K >= 1024 && ceil_div(M, 2 * BM) * ceil_div(N, 256) >= ctx->sm_count / 2;
   const bool pair = ctx->dbg_skip_kb < 0 && !batched && bn == 256 && M >= 256 && (pair_shape || g_check_pair || getenv("TALOS_TC_FORCE_PAIR")) && !getenv("TALOS_TC_NO_PAIR");
   g.m_tiles = (int)ceil_div(M, pair ? 2 * BM : BM); g.n_tiles = (int)ceil_div(N, bn); g.kb_total = (int)ceil_div(K, BK);
+  // Groups of 8 row panels once there are enough tiles for the order to matter (with ~148 tiles in flight an 8-wide
+  // group makes each wave touch 8 row panels and ~n/8 column panels instead of every row panel).
+  g.group_m = (g.m_tiles >= 16 && g.n_tiles >= 4 && !getenv("TALOS_TC_NO_RASTER")) ? 8 : g.m_tiles;
   int tiles = g.m_tiles * g.n_tiles, splits = 1;
   const int workers = pair ? ctx->sm_count / 2 : ctx->sm_count;   // CTAs, or CTA pairs
   // Split K when the output tiles alone cannot occupy the workers.  The tensor core truncates when it adds into the

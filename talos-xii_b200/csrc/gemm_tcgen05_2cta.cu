@@ -103,7 +103,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); if (BPS) prefetch_tmap(&tmap_b_lo);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (int it = pair; it < items && ok; it += npairs) {
-        const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+        const int ks = it / tiles_mn, rem = it % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
         const int row0 = mb * 2 * BM + (int)rank * BM, col0 = nb * BN + (int)rank * BH;
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -178,7 +178,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const uint32_t tempty_leader[2] = {map_to_cta(smem_u32(tempty + 0), 0), map_to_cta(smem_u32(tempty + 1), 0)};
     int tcount = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = pair; it < items && ok; it += npairs) {
-      const int ks = it / tiles_mn, rem = it % tiles_mn, nb = rem / g.m_tiles, mb = rem % g.m_tiles;
+      const int ks = it / tiles_mn, rem = it % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
       const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
       const int run = tcount & 1, other = run ^ 1; ++tcount;
       const int ckb = g.chain_kb > 0 ? g.chain_kb : (kb1 - kb0);

@@ -18,6 +18,7 @@ struct TcArgs {
   int chain_kb;                            // CTA-pair 3xTF32 kernel: k-blocks per accumulation chain folded on chip (0: one chain per item)
   int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
   long long stride_c;                      // elements between consecutive batch members of C
+  int group_m;                             // tile order: m-tiles are walked in groups of this many per column sweep (L2 reuse); >= m_tiles: plain order
   unsigned wait_spins;                     // poll limit of every bounded wait (WAIT_SPINS unless a test shortened it)
   int dbg_skip_kb;                         // test hook: CTA 0's producer never loads this k-block of its first item (-1: off)
 };
@@ -28,6 +29,17 @@ constexpr int BM = 128;                 // tile rows = TMEM lanes
 constexpr int BK = 32;                  // fp32 per 128-byte swizzle row
 constexpr int UMMA_K = 8;               // K per tcgen05.mma.kind::tf32
 constexpr uint32_t WAIT_SPINS = 1u << 22;
+
+// Output-tile order.  Tile `rem` of the m_tiles x n_tiles grid: the m index runs fastest inside a group of `group_m`
+// row panels, then the column panel advances, then the next group starts -- so the tiles in flight at any time (one
+// per CTA, consecutive `rem`) cover a near-square block of the result and re-use each other's operand panels in L2,
+// instead of every wave streaming all of A.
+__device__ __forceinline__ void tc_tile_coords(int rem, int m_tiles, int n_tiles, int group_m, int& mb, int& nb) {
+  if (group_m >= m_tiles) { nb = rem / m_tiles; mb = rem - nb * m_tiles; return; }
+  const int gsz = group_m * n_tiles, grp = rem / gsz, first_m = grp * group_m;
+  const int gm = min(group_m, m_tiles - first_m), within = rem - grp * gsz;
+  nb = within / gm; mb = first_m + within - nb * gm;
+}
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -258,18 +270,26 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensor
   const uint32_t t_row = t_base + ((uint32_t)(quad * 32) << 16);
   const int rows_valid = (int)min((long long)32, (long long)g.M - m0);
   constexpr int HALF_COLS = (EPI_WARPS == 8 && BN >= 64) ? BN / 2 : BN;
+  const int c_begin = half * HALF_COLS, c_end = min((half + 1) * HALF_COLS, BN);
+  if (rows_valid <= 0) return;
+  if (g.tma_out) {
+    // Results leave through TMA stores.  The wait for the previous chunk's TMA store (which is still reading the
+    // staging buffer) comes AFTER this chunk's epilogue arithmetic, just before the buffer is overwritten, so the
+    // store engine's read overlaps the arithmetic.  (Also keeping the next chunk's TMEM load in flight during the
+    // arithmetic was tried: 64 live accumulator registers made every variant spill.)
+    int c0 = c_begin;
+    bool have = c0 < c_end && (long long)nb * BN + c0 < g.N;
 #pragma unroll 1
-  for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 32) {
-    const long long n0 = (long long)nb * BN + c0;
-    if (n0 >= g.N || rows_valid <= 0) break;               // uniform across the warp
-    uint32_t r[32];
-    tmem_ld32(t_row + (uint32_t)c0, r);
-    tmem_ld_wait();
-    if (g.tma_out) {
+    while (have) {
+      const long long n0 = (long long)nb * BN + c0;
+      uint32_t r[32];
+      tmem_ld32(t_row + (uint32_t)c0, r);
+      tmem_ld_wait();
+      const int c1 = c0 + 32;
+      const bool have_next = c1 < c_end && (long long)nb * BN + c1 < g.N;
       // Fused epilogue in registers, then a 128B-swizzled 32x32 tile in shared memory that one
       // lane hands to the TMA store engine (clipped to [M,N] by the tensor map).
       float* buf = stage;
-      if (store_count >= 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
       {
         const bool fuse = (g.splits == 1) && (lane < rows_valid);
         const long long m = m0 + lane;
@@ -278,31 +298,49 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensor
         const float* aux_p = (fuse && dact) ? g.epi.aux_in + m * g.epi.ld_aux_in + n0 : nullptr;
         const float* cold_p = (fuse && g.epi.beta) ? c_base + m * g.ldc + n0 : nullptr;
         const int groups = (int)min((long long)8, (g.N - n0) >> 2);     // N is a multiple of 4 on this path
-#define TALOS_EPI_STORE(A, D)                                                                                           \
+#define TALOS_EPI_MATH(A, D)                                                                                            \
   _Pragma("unroll") for (int c = 0; c < 8; ++c) {                                                                      \
-float4 v = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),    \
-                       __uint_as_float(r[4 * c + 3]));                                                             \
-if (fuse && c < groups)                                                                                             \
+if (fuse && c < groups) {                                                                                           \
+  float4 v = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),  \
+                         __uint_as_float(r[4 * c + 3]));                                                           \
   v = epilogue_group<A, D>(v, bias_p ? bias_p + 4 * c : nullptr, aux_p ? aux_p + 4 * c : nullptr,                  \
                            cold_p ? cold_p + 4 * c : nullptr);                                                      \
-*(float4*)(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) = v;                                                          \
+  r[4 * c] = __float_as_uint(v.x); r[4 * c + 1] = __float_as_uint(v.y); r[4 * c + 2] = __float_as_uint(v.z);        \
+  r[4 * c + 3] = __float_as_uint(v.w);                                                                              \
+}                                                                                                                   \
   }
         switch (fuse ? g.epi.act * 4 + dact : 0) {
-          case 1: TALOS_EPI_STORE(0, 1) break;
-          case 2: TALOS_EPI_STORE(0, 2) break;
-          case 3: TALOS_EPI_STORE(0, 3) break;
-          case 4: TALOS_EPI_STORE(1, 0) break;
-          case 8: TALOS_EPI_STORE(2, 0) break;
-          case 12: TALOS_EPI_STORE(3, 0) break;
-          default: TALOS_EPI_STORE(0, 0) break;
+          case 1: TALOS_EPI_MATH(0, 1) break;
+          case 2: TALOS_EPI_MATH(0, 2) break;
+          case 3: TALOS_EPI_MATH(0, 3) break;
+          case 4: TALOS_EPI_MATH(1, 0) break;
+          case 8: TALOS_EPI_MATH(2, 0) break;
+          case 12: TALOS_EPI_MATH(3, 0) break;
+          default: if (g.epi.bias || g.epi.beta) { TALOS_EPI_MATH(0, 0) } break;
         }
-#undef TALOS_EPI_STORE
+#undef TALOS_EPI_MATH
       }
+      if (store_count >= 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *(float4*)(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) =
+            make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]), __uint_as_float(r[4 * c + 3]));
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) { tma_store_3d(tmap_c, buf, (int)n0, (int)m0, ks + bz); tma_store_commit(); }
       ++store_count;
-    } else {
+      c0 = c1; have = have_next;
+    }
+    return;
+  }
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+    const long long n0 = (long long)nb * BN + c0;
+    if (n0 >= g.N) break;                                   // uniform across the warp
+    uint32_t r[32];
+    tmem_ld32(t_row + (uint32_t)c0, r);
+    tmem_ld_wait();
+    {
       // Unaligned output: transpose through a padded tile so lanes run along the contiguous axis.
 #pragma unroll
       for (int j = 0; j < 32; ++j) stage[lane * 32 + (j ^ lane)] = __uint_as_float(r[j]);    // XOR-swizzled transpose tile
