@@ -41,7 +41,8 @@ template <bool X3, bool BPS> struct TcRoles {
   static constexpr int THREADS = (2 + EPI_WARPS + CONV_WARPS) * 32;       // 448 (3xTF32) or 320 (TF32)
 };
 
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false>
+// SBUF: staging buffers per epilogue warp (2 where the configuration leaves the shared memory for it).
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
 __global__ void __launch_bounds__((TcRoles<X3, BPS>::THREADS), MINB)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, TcArgs g) {
@@ -55,7 +56,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* sAlo = sB + STAGES * B_BYTES;
   uint8_t* sBlo = sAlo + (X3 ? STAGES * A_BYTES : 0);
   float* stage_all = (float*)(sBlo + (X3 ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
-  uint64_t* bars = (uint64_t*)(stage_all + 8 * 32 * 32);
+  uint64_t* bars = (uint64_t*)(stage_all + 8 * 32 * 32 * SBUF);
   uint64_t* full = bars;                   // TMA -> (converter | issuer)
   uint64_t* conv = full + STAGES;          // converter -> issuer (X3)
   uint64_t* empty = conv + STAGES;         // issuer (commit) -> TMA
@@ -110,7 +111,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (++pf_kb >= pf_kb1) { pf_it += gridDim.x; pf_decode(); }
       };
       const bool pf_on = g.pf_a || g.pf_b;
-      const bool b_resident = BPS && g.kb_total == 1 && g.n_tiles == 1 && g.batch == 1 && g.splits == 1;
+      const bool b_resident = BPS && g.kb_total <= STAGES && STAGES % g.kb_total == 0 && g.n_tiles == 1 && g.batch == 1 && g.splits == 1;
       int issued = 0;
       if (pf_on) { pf_decode(); for (int i = 0; i < PF_DIST; ++i) pf_step(); }
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
@@ -123,8 +124,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // Test hook: this stage is never armed nor loaded, so its consumers' bounded waits run out and the CTA
           // leaves through the abort path (nothing faults; the loads already in flight land and are ignored).
           if (g.dbg_skip_kb >= 0 && blockIdx.x == 0 && it == 0 && kb - kb0 == g.dbg_skip_kb) { if (++stage == STAGES) { stage = 0; phase ^= 1; } continue; }
-          // A one-k-block product with a single column panel (the K = 32 input gradient of the fused heads) uses the
-          // SAME B tile for every output tile: each stage's B buffers are filled on the stage's first use and kept.
+          // A product with a single column panel whose k-blocks divide the stage count (K = 32: the input gradient of the
+          // fused heads; K = 64 with two stages: the first layer) meets the SAME B tile every time it comes back to a
+          // stage: each stage's B buffers are filled on the stage's first use and kept.
           const bool load_b = !b_resident || issued < STAGES;
           ++issued;
           mbar_expect_tx(full + stage, A_BYTES + (load_b ? B_BYTES + (BPS ? B_BYTES : 0) : 0));
@@ -194,7 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int ks = r / tiles_mn, rem = r % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
       if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
       tc_fence_after();
-      tc_epilogue_tile<BN, EPI_WARPS>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32), (long long)mb * BM, nb, ks, bz, store_count);
+      tc_epilogue_tile<BN, EPI_WARPS, SBUF>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32 * SBUF), (long long)mb * BM, nb, ks, bz, store_count);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + acc);
@@ -314,27 +316,27 @@ bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t r
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, bool X3>
+template <int BN, int STAGES, bool X3, int SBUF = 1>
 size_t tc_smem_bytes() {
-  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + 8 * 32 * 32 * 4 + (3 * STAGES + 4) * 8 + 16 + 1024;
+  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + 8 * 32 * 32 * 4 * SBUF + (3 * STAGES + 4) * 8 + 16 + 1024;
 }
 
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false>
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
 void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tbl, const TcArgs& g, int grid) {
-  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS>;
-  size_t smem = tc_smem_bytes<BN, STAGES, X3>();
+  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF>;
+  size_t smem = tc_smem_bytes<BN, STAGES, X3, SBUF>();
   TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<grid, TcRoles<X3, BPS>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
   talos_launched(ctx, "gemm_tcgen05");
 }
 
-template <int BN, int STAGES, bool X3, int MINB = 1, bool BPS = false>
+template <int BN, int STAGES, bool X3, int MINB = 1, bool BPS = false, int SBUF = 1>
 void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tbl,
                   const TcArgs& g, int grid) {
-  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
-  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
-  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
-  else launch_one<BN, STAGES, X3, true, true, MINB, BPS>(ctx, ta, tb, tc, tbl, g, grid);
+  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
+  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
+  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
+  else launch_one<BN, STAGES, X3, true, true, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
 }
 
 static inline bool x3_mode(int mode) { return mode == TALOS_MODE_TF32X3; }
@@ -350,6 +352,11 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   const bool b_given = extra && extra->b_hi && !batched && (x3_mode(mode) ? extra->b_lo != nullptr : true);
   const bool a_mn = (opA == TALOS_OP_T), b_mn = (opB == TALOS_OP_N), x3 = (mode == TALOS_MODE_TF32X3);
   int bn = N > 128 ? 256 : N > 64 ? 128 : N > 32 ? 64 : 32;
+  // Short reductions with a prepared small B (K <= 64: the first layer's forward product) are all epilogue: 128-column
+  // tiles leave the shared memory for two staging buffers per epilogue warp, so that the store engine's read of one
+  // chunk overlaps the arithmetic of the next.
+  const bool short_k = !batched && x3 && bn == 256 && K <= 64 && (b_given || (opB == TALOS_OP_N ? K * N : N * K) <= (1 << 20)) && !getenv("TALOS_TC_NO_SHORTK");
+  if (short_k) bn = 128;
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
@@ -472,13 +479,15 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
     return;
   }
   int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count);
-#define TALOS_TC_CASE(BNv, ST, ST3)                                                                          \
-  if (bn == BNv) {                                                                                           \
-    if (x3 && presplit) launch_major<BNv, ST3, true, 1, true>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);    \
-    else if (x3) launch_major<BNv, ST3, true>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                     \
-    else launch_major<BNv, ST, false>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                             \
+  // (tile width, stages and staging buffers per epilogue warp in TF32 mode, the same for the 3xTF32 kernels)
+#define TALOS_TC_CASE(BNv, ST, SB, ST3, SB3)                                                                      \
+  if (bn == BNv) {                                                                                                \
+    if (x3 && presplit) launch_major<BNv, ST3, true, 1, true, SB3>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);    \
+    else if (x3) launch_major<BNv, ST3, true, 1, false, SB3>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);           \
+    else launch_major<BNv, ST, false, 1, false, SB>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                    \
   }
-  TALOS_TC_CASE(256, 4, 2) else TALOS_TC_CASE(128, 6, 3) else TALOS_TC_CASE(64, 8, 4) else TALOS_TC_CASE(32, 8, 4)
+  if (short_k && presplit) launch_major<128, 2, true, 1, true, 2>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);
+  else TALOS_TC_CASE(256, 3, 2, 2, 1) else TALOS_TC_CASE(128, 6, 1, 3, 1) else TALOS_TC_CASE(64, 8, 1, 4, 1) else TALOS_TC_CASE(32, 8, 2, 4, 2)
 #undef TALOS_TC_CASE
   if (splits > 1 && !keep_partials) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
 }

@@ -259,7 +259,9 @@ __device__ __forceinline__ void tc_fold_chain(uint32_t t_run, uint32_t t_acc, in
 // One epilogue warp's share of a finished 128 x BN accumulator: warp w (2..9) owns TMEM lane quadrant w%4 (32 rows,
 // one per lane) and half of the columns, drained 32 columns at a time.  `t_base` is the TMEM address of the
 // accumulator's first column, `m_base` the global row of TMEM lane 0, `stage` this warp's 4 KB staging buffer.
-template <int BN, int EPI_WARPS = 8>
+// SBUF staging buffers per warp (consecutive 4 KB blocks at `stage`): with two, the store engine may still be reading
+// the previous chunk while the next one is written.
+template <int BN, int EPI_WARPS = 8, int SBUF = 1>
 __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensorMap* tmap_c, uint32_t t_base, int warp, int lane, float* stage,
                                                  long long m_base, int nb, int ks, int bz, uint32_t& store_count) {
   static_assert(EPI_WARPS == 8 || EPI_WARPS == 4, "two warps per TMEM lane quadrant, or one");
@@ -289,7 +291,7 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensor
       const bool have_next = c1 < c_end && (long long)nb * BN + c1 < g.N;
       // Fused epilogue in registers, then a 128B-swizzled 32x32 tile in shared memory that one
       // lane hands to the TMA store engine (clipped to [M,N] by the tensor map).
-      float* buf = stage;
+      float* buf = stage + (SBUF == 2 ? (store_count & 1u) * (32 * 32) : 0);
       {
         const bool fuse = (g.splits == 1) && (lane < rows_valid);
         const long long m = m0 + lane;
@@ -320,7 +322,7 @@ if (fuse && c < groups) {                                                       
         }
 #undef TALOS_EPI_MATH
       }
-      if (store_count >= 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+      if (store_count >= SBUF) { if (lane == 0) tma_store_wait_read<SBUF - 1>(); __syncwarp(); }
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         *(float4*)(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) =
