@@ -2,7 +2,7 @@
 """Benchmark of the hot path: the data-parallel PPO actor-critic update of benchmark configuration 5.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference] [--mode tf32x3|tf32|fp32]
-                    [--sections ppo,gemm,hbm,cpu]
+                    [--sections ppo,gemm,hbm,cpu,host]
 
 A step is one optimizer step: forward, per-sample PPO loss, backward, gradient all-reduce (N > 1)
 and Adam on one minibatch of 65 536 transitions PER GPU (obs 64 -> 256 -> 256 tanh trunk, 16-way
@@ -329,6 +329,58 @@ def hbm_section(talos, ctx, timer, pk, pk_kind, local, reps=20):
     return out
 
 
+def host_route_section(mode):
+    """The two training routes that go through the Tensor / autograd mirror of the crate's API rather than the fused PPO
+    trainer -- a dueling double-DQN train step at batch 64 (src/dqn.rs:482-584) and a LuckTransformer(8, 64) forward +
+    backward on [64, 16, 8] -- timed by the C++ host program (host clock between two stream synchronisations), with the
+    oracle's time for the same arithmetic on the host cores beside it.  Every tensor of those routes comes from the
+    context's caching allocator; the counters show whether the timed loop reached the CUDA driver."""
+    exe = os.path.join(ROOT, "tests", "cpp", "bin", "host_driver")
+    if not os.path.exists(exe):
+        return {"unavailable": "tests/cpp/bin/host_driver is not built"}
+    r = subprocess.run([exe, "time", str(mode), os.devnull, "7", "200", "64"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    if r.returncode != 0:
+        return {"unavailable": "host_driver failed: " + r.stdout[-300:]}
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    import numpy as np
+    import oracle as orc
+    from oracle import model as om
+    th = os.cpu_count() or 1
+    lt = om.LuckTransformer(8, 64, 7); x = orc.f32r(orc.lcg_rand((64, 16, 8), -0.5, 0.5, 10)); g = np.full((64, 16, 64), 1.0 / (64 * 16 * 64))
+    lt.forward_backward(x, g)
+    t0 = time.perf_counter(); n = 0
+    while n < 3 or time.perf_counter() - t0 < 1.0:
+        lt.forward_backward(x, g); n += 1
+    out["cpu_oracle_luck_fwd_bwd_ms"] = (time.perf_counter() - t0) / n * 1e3
+    # the DQN step's arithmetic with the oracle's pieces: three forwards, targets, loss, backward, clipped Adam, soft update
+    W = [om.linear_init_lcg(8, 64, True, 7), om.linear_init_lcg(64, 64, True, 8), om.linear_init_lcg(64, 1, True, 9), om.linear_init_lcg(64, 5, True, 10)]
+    P = [np.array(t) for w in W for t in w]; T = [p.copy() for p in P]; m = [np.zeros_like(p) for p in P]; v = [np.zeros_like(p) for p in P]
+    s0 = orc.lcg_rand((64, 8), -1.0, 1.0, 8); s1 = orc.lcg_rand((64, 8), -1.0, 1.0, 9)
+    act = np.arange(64) % 5; rew = 0.1 * (np.arange(64) % 7) - 0.3; done = (np.arange(64) % 9 == 0).astype(np.float64)
+
+    def fwd(Q, s):
+        z1 = om.linear_fwd(s, Q[0], Q[1]); h1 = np.maximum(z1, 0); z2 = om.linear_fwd(h1, Q[2], Q[3]); h2 = np.maximum(z2, 0)
+        return (z1, h1, z2, h2), om.dueling_combine(om.linear_fwd(h2, Q[4], Q[5]), om.linear_fwd(h2, Q[6], Q[7]))
+
+    def dqn_step(t):
+        (z1, h1, z2, h2), q = fwd(P, s0); _, qe = fwd(P, s1); _, qt = fwd(T, s1)
+        _, dq = om.dqn_loss_fwd_bwd(q, act, om.dqn_target(qe, qt, rew, done))
+        dv, da = om.dueling_combine_bwd(dq)
+        dh_v, gWv, gbv = om.linear_bwd(h2, P[4], dv, True); dh_a, gWa, gba = om.linear_bwd(h2, P[6], da, True)
+        d2 = (dh_v + dh_a) * (z2 > 0); dh1, gW2, gb2 = om.linear_bwd(h1, P[2], d2, True)
+        d1 = dh1 * (z1 > 0); _, gW1, gb1 = om.linear_bwd(s0, P[0], d1, True, need_dx=False)
+        om.adam_step(P, [gW1, gb1, gW2, gb2, gWv, gbv, gWa, gba], m, v, t, 1e-3, clip_norm=1.0)
+        for i in range(len(T)):
+            T[i] = om.soft_update(T[i], P[i], 0.005)
+    dqn_step(1)
+    t0 = time.perf_counter(); n = 0
+    while n < 5 or time.perf_counter() - t0 < 1.0:
+        n += 1; dqn_step(n + 1)
+    out["cpu_oracle_dqn_train_step_ms"] = (time.perf_counter() - t0) / n * 1e3
+    out["cpu_threads"] = th; out["cpu"] = cpu_model(); out["mode"] = mode
+    return out
+
+
 def params_digest(tr):
     import hashlib
     import numpy as np
@@ -422,12 +474,13 @@ def run_ours(args):
     if args.kernel_only:                 # profiling aid: only the dominant kernel runs (`ncu --profile-from-start off -k regex:gemm_tc`)
         print(json.dumps({"kernel_only_ms": dominant_kernel(talos, ctx, mode, MB, timer, reps=3, profile=True)["ms"]}))
         return
-    sections = set(args.sections.split(",")) if args.sections else {"ppo", "gemm", "hbm", "cpu"}
+    sections = set(args.sections.split(",")) if args.sections else {"ppo", "gemm", "hbm", "cpu", "host"}
     pk, pk_kind = peaks()
     if "ppo" not in sections:            # kernel figures only (what the committed profiles' commands run)
         out = {}
         if "gemm" in sections: out["gemm"] = gemm_section(talos, ctx, timer, pk, pk_kind, local)
         if "hbm" in sections: out["hbm_kernels"] = hbm_section(talos, ctx, timer, pk, pk_kind, local)
+        if "host" in sections: out["host_autograd_routes"] = host_route_section(mode)
         print(json.dumps(out), flush=True)
         return
     obs_h, act_h, adv_h, ret_h = synth_shard(talos, rank, world)
@@ -512,7 +565,7 @@ def run_ours(args):
         dp = data_parallel_checks(talos, ctx, comm, dist, rank, world, mode, params)
 
     # ---- the dominant kernel alone: the 65536 x 256 x 256 tensor-core GEMM (three of them per step: layer-2 forward, dH1, dW2)
-    roof = None; other_modes = {}; gemm = None; hbm = None
+    roof = None; other_modes = {}; gemm = None; hbm = None; host_route = None
     if rank == 0:
         M, N, K = mb, HID, HID
         ksamp = ClockSampler(local)
@@ -544,6 +597,8 @@ def run_ours(args):
             gemm = gemm_section(talos, ctx, timer, pk, pk_kind, local)
         if world == 1 and "hbm" in sections:
             hbm = hbm_section(talos, ctx, timer, pk, pk_kind, local)
+        if world == 1 and "host" in sections:
+            host_route = host_route_section(mode)
 
     cpu = None
     if rank == 0 and world == 1 and "cpu" in sections and not args.no_cpu:
@@ -564,6 +619,8 @@ def run_ours(args):
             out["gemm"] = gemm
         if hbm is not None:
             out["hbm_kernels"] = hbm
+        if host_route is not None:
+            out["host_autograd_routes"] = host_route
         print(json.dumps(out), flush=True)
     tr.close()
     if comm is not None:
@@ -580,7 +637,7 @@ def main():
     ap.add_argument("--repeats", type=int, default=10, help="how many times the timed region of --steps steps is run (value = the median region)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="tf32x3", choices=["tf32x3", "tf32", "fp32"])
-    ap.add_argument("--sections", default="", help="comma list of ppo,gemm,hbm,cpu (default: all; without ppo only the kernel figures are printed)")
+    ap.add_argument("--sections", default="", help="comma list of ppo,gemm,hbm,cpu,host (default: all; without ppo only the kernel figures are printed)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--kernel-only", action="store_true", help="run only the dominant kernel (profiling aid)")
     args = ap.parse_args()

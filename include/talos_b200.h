@@ -331,6 +331,14 @@ talos_status talos_adam_step(talos_ctx* ctx, float* params, const float* grads, 
                              int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
                              float clip_norm);
 
+/* The DQN optimizer's step on ONE tensor of a model whose global gradient norm spans several tensors
+ * (src/dqn.rs:209-222 sums g^2 over ALL parameters first): sumsq_dev[0] (device) holds that sum -- e.g. accumulated
+ * with talos_dot(g, g, n, sumsq, 1) per tensor -- and the step scales g by clip_norm / sqrt(sum) when the norm exceeds
+ * clip_norm.  Nothing comes back to the host. */
+talos_status talos_adam_step_global_clip(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
+                                         int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
+                                         const float* sumsq_dev, float clip_norm);
+
 /* ---- seeded synthetic inputs: src/rng.rs:14-117 (SplitMix64 -> xoshiro256**) on the host ---- */
 talos_status talos_rng_uniform_host(uint64_t seed, float lo, float hi, float* out_host, int64_t n);
 talos_status talos_rng_normal_host(uint64_t seed, float mean, float std, float* out_host, int64_t n);

@@ -182,6 +182,21 @@ void talos_adam_launch(talos_ctx* ctx, float* params, const float* grads, float*
   talos_launched(ctx, "adam");
 }
 
+TALOS_API talos_status talos_adam_step_global_clip(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
+                                                   int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
+                                                   const float* sumsq_dev, float clip_norm) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(n >= 0 && t >= 1 && clip_norm > 0.f, TALOS_ERR_ARG, "Adam step number must be >= 1 and the clip norm positive");
+  if (n == 0) return TALOS_OK;
+  TALOS_REQUIRE(params && grads && m && v && sumsq_dev, TALOS_ERR_ARG, "null pointer");
+  const double bc1 = 1.0 - pow((double)beta1, (double)t), bc2 = 1.0 - pow((double)beta2, (double)t);
+  adam_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(params, grads, m, v, n, lr, beta1, beta2, eps, (float)(1.0 / bc1), (float)(1.0 / bc2),
+                                                                  grad_scale, sumsq_dev, 1, clip_norm, nullptr, nullptr);
+  talos_launched(ctx, "adam_global_clip");
+  TALOS_ENTRY_END
+}
+
 TALOS_API talos_status talos_adam_step(talos_ctx* ctx, float* params, const float* grads, float* m, float* v, int64_t n,
                                        int64_t t, float lr, float beta1, float beta2, float eps, float grad_scale,
                                        float clip_norm) {

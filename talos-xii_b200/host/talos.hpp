@@ -723,19 +723,23 @@ struct BatchedRollout {
 };
 
 struct Adam {                                                                       // src/ppo.rs:482-540; clip_norm = 1 gives src/dqn.rs:207-239
-  std::vector<Tensor> params; std::vector<Buf> m, v; size_t t = 0; double lr, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, clip_norm = 0.0;
+  std::vector<Tensor> params; std::vector<Buf> m, v; Buf sumsq; size_t t = 0; double lr, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, clip_norm = 0.0;
   Adam(std::vector<Tensor> p, double learning_rate) : params(std::move(p)), lr(learning_rate) { for (auto& q : params) { m.push_back(make_buf(q.len())); v.push_back(make_buf(q.len())); } }
   void set_lr(double l) { lr = l; }
   void step() {
     ++t;
-    float scale = 1.f;
-    if (clip_norm > 0.0) {                                                          // global norm over ALL parameters first
-      double total = 0.0; for (auto& p : params) for (double g : p.grad_vec()) total += g * g;
-      total = std::sqrt(total); if (total > clip_norm) scale = (float)(clip_norm / total);
+    if (clip_norm > 0.0) {                                                          // global norm over ALL parameters first, on the device
+      if (!sumsq) sumsq = make_buf(1);
+      check(talos_memset_zero(ctx(), sumsq->dev, sizeof(float)));
+      for (auto& p : params) check(talos_dot(ctx(), p.g(), p.g(), (int64_t)p.len(), sumsq->dev, 1));
+      for (size_t i = 0; i < params.size(); ++i)
+        check(talos_adam_step_global_clip(ctx(), params[i].d(), params[i].g(), m[i]->dev, v[i]->dev, (int64_t)params[i].len(), (int64_t)t, (float)lr, (float)beta1,
+                                          (float)beta2, (float)eps, 1.f, sumsq->dev, (float)clip_norm));
+      return;
     }
     for (size_t i = 0; i < params.size(); ++i)
       check(talos_adam_step(ctx(), params[i].d(), params[i].g(), m[i]->dev, v[i]->dev, (int64_t)params[i].len(), (int64_t)t, (float)lr, (float)beta1, (float)beta2,
-                            (float)eps, scale, 0.f));
+                            (float)eps, 1.f, 0.f));
   }
   void zero_grad() const { for (auto& p : params) p.zero_grad(); }
 };

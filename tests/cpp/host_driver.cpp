@@ -12,6 +12,10 @@
 //                                        (JSON), read back from each and through load_ppo_model (binary first; JSON when
 //                                        only <prefix>.json_only exists); writes f64 actor logits on LCG states [B,S,8] of the
 //                                        original and of the four loaded models, [5][B,5].
+//   time  <seed> <iters> <batch>       : no dump; times the two training routes that go through the Tensor tape -- a dueling
+//                                        double-DQN train step at batch `batch` (forward x3, loss, backward, clipped Adam, soft
+//                                        update: src/dqn.rs:482-584) and a LuckTransformer(8, 64) forward + backward on
+//                                        [batch, 16, 8] -- and prints one JSON line with steps per second and the allocator's counters.
 //   rollout <seed> <N> <T> <ctx> [time]: ActorCritic(seed) stepped T times over N simulations through BatchedRollout
 //                                        (KV rings of ctx+1 slots); states N(0, 0.5^2) seed+500 as [T,N,8]; simulation n
 //                                        ends an episode after step t when (t*7 + n*3) % 11 == 0; writes f64 probabilities
@@ -97,6 +101,38 @@ int main(int argc, char** argv) {
       for (const ActorCritic* m : {&ac, &from_bin, &from_json, &*loaded, &*loaded_json}) dump(f, m->forward_actor(x).to_vec());
       // a second save of a loaded model must reproduce the files byte for byte
       if (serde::to_bincode(from_json) != std::vector<uint8_t>(raw.begin(), raw.end()) || serde::to_json(from_bin) != js) { std::fprintf(stderr, "host_driver: re-serialised model differs\n"); return 8; }
+    } else if (what == "time") {
+      const size_t iters = B, batch = S;
+      DuelingQNetwork policy(seed), target(seed);
+      Tensor states = Tensor::rand({batch, 8}, -1.0, 1.0, seed + 1), next = Tensor::rand({batch, 8}, -1.0, 1.0, seed + 2);
+      std::vector<int32_t> actions(batch); std::vector<double> rewards(batch), dones(batch);
+      for (size_t i = 0; i < batch; ++i) { actions[i] = (int32_t)(i % 5); rewards[i] = 0.1 * (double)(i % 7) - 0.3; dones[i] = (i % 9 == 0) ? 1.0 : 0.0; }
+      Adam opt(policy.parameters(), 1e-3); opt.clip_norm = 1.0;
+      auto dqn_step = [&]() {
+        opt.zero_grad();
+        Tensor loss = dqn_loss(policy.forward(states), actions, policy.forward(next), target.forward(next), rewards, dones);
+        loss.backward(); opt.step(); target.soft_update(policy, 0.005);
+      };
+      auto timed = [&](auto&& fn) {
+        for (int i = 0; i < 3; ++i) fn();
+        Runtime::get().synchronize();
+        const auto t0 = std::chrono::steady_clock::now();
+        for (size_t i = 0; i < iters; ++i) fn();
+        Runtime::get().synchronize();
+        return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() / (double)iters;
+      };
+      int64_t st0[4], st1[4];
+      const double dqn_s = timed(dqn_step);
+      LuckTransformer lt(8, 64, true, seed); Tensor x = Tensor::rand({batch, 16, 8}, -0.5, 0.5, seed + 3);
+      auto params = lt.parameters();
+      auto luck_step = [&]() { for (auto& p : params) p.zero_grad(); lt.forward(x).mean().backward(); };
+      luck_step(); Runtime::get().synchronize();
+      check(talos_ctx_memory_stats(ctx(), st0));
+      const double luck_s = timed(luck_step);
+      check(talos_ctx_memory_stats(ctx(), st1));
+      std::printf("{\"dqn_train_step_ms\": %.4f, \"dqn_steps_per_s\": %.1f, \"luck_fwd_bwd_ms\": %.4f, \"batch\": %zu, \"iters\": %zu, "
+                  "\"luck_driver_allocations_while_timed\": %lld, \"luck_allocations_from_cache_while_timed\": %lld, \"cached_bytes\": %lld}\n",
+                  dqn_s * 1e3, 1.0 / dqn_s, luck_s * 1e3, batch, iters, (long long)(st1[2] - st0[2]), (long long)(st1[3] - st0[3]), (long long)st1[1]);
     } else if (what == "rollout") {
       const size_t N = B, T = S, ctx_len = std::stoul(argv[7]);
       const bool timing = argc > 8 && std::string(argv[8]) == "time";
