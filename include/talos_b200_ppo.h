@@ -40,6 +40,17 @@ talos_status talos_comm_init(talos_ctx* ctx, const uint8_t* id_host, int32_t nra
 talos_status talos_comm_destroy(talos_comm* comm);
 /* In-place sum over ranks of n floats, enqueued on the ctx stream. */
 talos_status talos_comm_allreduce_sum(talos_comm* comm, float* buf, int64_t n);
+/* 1 when the ranks of this communicator (one node, NVLink) have mapped each other's exchange areas, so that
+ * talos_ppo_step exchanges gradients with ONE kernel over peer memory -- publish, bounded wait, sum in rank order, Adam,
+ * weight preparation -- instead of an NCCL all-reduce followed by two more kernels; 0 when that could not be set up on
+ * some rank (or TALOS_COMM_NO_P2P is set) and the NCCL all-reduce serves.  The reference has no counterpart: it is a
+ * single process. */
+int32_t talos_comm_peer_exchange_active(talos_comm* comm);
+/* Test hook: skip_next_signal != 0 makes THIS rank leave out its publication in the next peer-memory exchange, so that
+ * the other ranks' bounded waits (wait_spins polls, 0 = default, else >= 1024) run out: they return by themselves,
+ * raise their context's error word (TALOS_ERR_TIMEOUT at the next blocking call) and leave their parameters untouched.
+ * Nothing faults or hangs.  The communicator must be destroyed afterwards (the ranks no longer agree). */
+talos_status talos_debug_comm_stall(talos_comm* comm, int32_t skip_next_signal, uint32_t wait_spins);
 
 /* ---- trainer --------------------------------------------------------------------------------- */
 talos_status talos_ppo_create(talos_ctx* ctx, const talos_ppo_config* cfg, talos_ppo** out);

@@ -114,7 +114,7 @@ class _Lib:
         return checked
 
 
-_NOT_STATUS = {"talos_ctx_tensor_cores_active", "talos_ctx_tensor_cores_state"}
+_NOT_STATUS = {"talos_ctx_tensor_cores_active", "talos_ctx_tensor_cores_state", "talos_comm_peer_exchange_active"}
 
 lib = _Lib()
 
@@ -203,6 +203,12 @@ class Comm:
         buf = (C.c_uint8 * 128).from_buffer_copy(uid)
         lib.talos_comm_init(ctx.handle, buf, nranks, rank, C.byref(h))
         self.handle, self.ctx, self.nranks, self.rank = h, ctx, nranks, rank
+
+    @property
+    def peer_exchange_active(self):
+        """True when the ranks have mapped each other's exchange areas (gradient exchange + Adam as one kernel over
+        NVLink peer memory); False when the NCCL all-reduce serves."""
+        return bool(lib.talos_comm_peer_exchange_active(self.handle))
 
     def allreduce_sum(self, dev_ptr, n):
         lib.talos_comm_allreduce_sum(self.handle, dev_ptr, n)

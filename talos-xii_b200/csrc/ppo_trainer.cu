@@ -2,8 +2,7 @@
 // for an MLP actor-critic, one fused sequence of GEMM / loss / Adam launches per minibatch.
 #include <vector>
 
-#include "common.cuh"
-#include "../../include/talos_b200_ppo.h"
+#include "comm.cuh"
 
 // internal launchers of other translation units
 void talos_adam_launch(talos_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, int64_t t, float lr, float b1,
@@ -168,7 +167,12 @@ void check(talos_ppo* p) { TALOS_REQUIRE(p != nullptr, TALOS_ERR_ARG, "null trai
 
 void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions, const float* old_logp, const float* adv,
           const float* ret, int64_t n) {
-  const auto& c = p->cfg; talos_ctx* ctx = p->ctx; const float* P = p->params; float* G = p->grads;
+  const auto& c = p->cfg; talos_ctx* ctx = p->ctx; const float* P = p->params;
+  // With the peer-memory exchange the step's gradient buffer IS this rank's exchange slot: the backward products write
+  // straight into memory the other ranks have mapped, and one kernel does exchange + Adam + weight preparation.
+  const bool peer = comm && comm->x.active && (size_t)(p->n_int + 4) <= comm->x.slot_floats && comm->ctx == ctx;
+  const uint64_t seq = peer ? comm->x.seq + 1 : 0;
+  float* G = peer ? comm->x.slot(comm->rank, seq) : p->grads;
   const int64_t H = c.hidden, HP = p->HP;
   const int64_t l0 = ctx->launches.load();
   float* tail = G + p->n_int;
@@ -224,12 +228,24 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
     gs.first_block[6] = blocks;
     if (blocks > 0) { grad_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(gs); talos_launched(ctx, "grad_gather"); }
   }
-  if (comm) { if ((st = talos_comm_allreduce_sum(comm, G, p->n_int + 4))) throw talos_error(st, talos_last_error_string()); }
   p->t += 1;
   float* stat_slot = p->step_stats + 4 * (p->steps_in_epoch % MAX_STEPS_PER_EPOCH);
-  talos_adam_launch(ctx, p->params, G, p->m, p->v, p->n_int, p->t, c.lr, c.beta1, c.beta2, c.eps, 1.0f, tail + 2, 0.f, stat_slot);
-  p->weights_prepared = false;
-  ensure_weights_prepared(p);                                  // for the next step's products (and the caller's next forward)
+  if (peer) {
+    XchgAdamArgs a{};
+    for (int r = 0; r < comm->nranks; ++r) { a.slot[r] = comm->x.slot(r, seq); a.peer_flags[r] = comm->x.flags(r); }
+    a.world = comm->nranks; a.rank = comm->rank; a.seq = seq; a.spins = comm->x.wait_spins; a.skip_signal = comm->x.dbg_skip_signal;
+    a.status = ctx->dev_status; a.params = p->params; a.m = p->m; a.v = p->v; a.w_hi = p->w_hi; a.w_lo = p->w_lo; a.grads_out = p->grads; a.stats_out = stat_slot;
+    a.n = p->n_int; a.lr = c.lr; a.b1 = c.beta1; a.b2 = c.beta2; a.eps = c.eps;
+    a.inv_bc1 = (float)(1.0 / (1.0 - pow((double)c.beta1, (double)p->t))); a.inv_bc2 = (float)(1.0 / (1.0 - pow((double)c.beta2, (double)p->t)));
+    talos_xchg_adam_launch(ctx, a);
+    comm->x.seq = seq; comm->x.dbg_skip_signal = 0;
+    p->weights_prepared = p->w_hi != nullptr;
+  } else {
+    if (comm) { if ((st = talos_comm_allreduce_sum(comm, G, p->n_int + 4))) throw talos_error(st, talos_last_error_string()); }
+    talos_adam_launch(ctx, p->params, G, p->m, p->v, p->n_int, p->t, c.lr, c.beta1, c.beta2, c.eps, 1.0f, tail + 2, 0.f, stat_slot);
+    p->weights_prepared = false;
+    ensure_weights_prepared(p);                                // for the next step's products (and the caller's next forward)
+  }
   p->steps_in_epoch += 1;
   p->last_launches = ctx->launches.load() - l0;
 }

@@ -1,7 +1,10 @@
 """Worker launched once per rank by the data-parallel tests (not a test module itself).
 
     python dp_worker.py cpu  <rank> <world> <port> <out.npz>     gloo ranks on CPU: the exchange protocol with the oracle's gradients
-    python dp_worker.py gpu  <rank> <world> <port> <out.npz>     one GPU per rank: the library's trainer + NCCL exchange
+    python dp_worker.py gpu  <rank> <world> <port> <out.npz>     one GPU per rank: the library's trainer and its gradient exchange (peer
+                                                                 memory, or NCCL with TALOS_COMM_NO_P2P=1)
+    python dp_worker.py gpu_stall <rank> <world> <port> <out.npz>  as gpu, but after one good step the LAST rank leaves out its publication
+                                                                 once: every other rank's bounded wait must run out and report TIMEOUT
 """
 import os
 import sys
@@ -73,10 +76,27 @@ def main():
     # gather this rank's slices of every global minibatch into one contiguous local shard
     idx = np.concatenate([np.arange(s + rank * mb_local, s + (rank + 1) * mb_local) for s in range(0, N, MB)])
     dev = lambda a, dt: torch.tensor(np.ascontiguousarray(a[idx]), dtype=dt, device="cuda")
-    kls = tr.update(dev(obs, torch.float32), dev(act, torch.int32), dev(old, torch.float32), dev(adv, torch.float32), dev(ret, torch.float32),
-                    idx.size, EPOCHS)
+    peer = bool(comm.peer_exchange_active) if comm else False
+    d = [dev(obs, torch.float32), dev(act, torch.int32), dev(old, torch.float32), dev(adv, torch.float32), dev(ret, torch.float32)]
+    if kind == "gpu_stall":
+        assert peer, "the stall scenario needs the peer-memory exchange"
+        tr.step(*d, mb_local); before = tr.get_params()                     # one good step
+        talos.lib.talos_debug_comm_stall(comm.handle, 1 if rank == world - 1 else 0, 200000)
+        tr.step(*[t[mb_local:] for t in d], mb_local)
+        status = 0
+        try:
+            tr.last_loss()
+        except talos.TalosError as e:
+            status = e.status
+        after = tr.get_params()
+        unchanged = all(np.array_equal(before[k], after[k]) for k in before)
+        dist.barrier()                                                      # every rank is between steps, nothing in flight
+        np.savez(out, status=status, unchanged=unchanged, peer=peer)
+        tr.close(); comm.close(); dist.destroy_process_group()
+        return
+    kls = tr.update(*d, idx.size, EPOCHS)
     got = tr.get_params()
-    np.savez(out, kls=np.array(kls), **{k: v.astype(np.float64) for k, v in got.items()})
+    np.savez(out, kls=np.array(kls), peer=peer, **{k: v.astype(np.float64) for k, v in got.items()})
     tr.close()
     if comm: comm.close()
     dist.destroy_process_group()

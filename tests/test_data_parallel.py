@@ -81,14 +81,19 @@ def test_two_gloo_ranks_equal_one_rank_on_the_global_batch():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", [0, 1])
-def test_two_gpu_ranks_equal_one_gpu_rank_and_the_oracle(mode):
+@pytest.mark.parametrize("mode,path", [(0, "peer"), (1, "peer"), (1, "nccl")])
+def test_two_gpu_ranks_equal_one_gpu_rank_and_the_oracle(mode, path):
+    # both gradient exchanges: the fused peer-memory kernel (sum in rank order + Adam + weight preparation) and the NCCL
+    # all-reduce it replaces
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ref, ref_kls = single_rank_reference()
     env = {"TALOS_TEST_MODE": str(mode), "NCCL_NVLS_ENABLE": "0"}
+    if path == "nccl":
+        env["TALOS_COMM_NO_P2P"] = "1"
     two = launch("gpu", 2, env); one = launch("gpu", 1, env)
+    assert bool(two[0]["peer"]) == (path == "peer") and bool(two[1]["peer"]) == (path == "peer")
     for k in ref:
         assert np.array_equal(two[0][k], two[1][k]), "ranks diverged: " + k
         d = np.linalg.norm(ref[k]); d = d if d > 0 else 1.0
@@ -96,3 +101,15 @@ def test_two_gpu_ranks_equal_one_gpu_rank_and_the_oracle(mode):
         if k.startswith("w"):
             assert np.linalg.norm(two[0][k] - ref[k].reshape(two[0][k].shape)) <= 1e-5 * d, k
     assert np.allclose(two[0]["kls"], ref_kls, rtol=1e-3, atol=1e-8)
+
+
+@pytest.mark.gpu
+def test_a_rank_that_never_publishes_makes_the_others_give_up_cleanly():
+    # failure detection without a fault: the last rank skips one publication (a host-side switch); the other rank's
+    # bounded wait runs out, its kernel returns, the error word surfaces as TALOS_ERR_TIMEOUT and its weights are untouched
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = launch("gpu_stall", 2, {"TALOS_TEST_MODE": "1", "NCCL_NVLS_ENABLE": "0"})
+    assert bool(res[0]["peer"]) and int(res[0]["status"]) == 6 and bool(res[0]["unchanged"])      # rank 0 gave up: TALOS_ERR_TIMEOUT
+    assert int(res[1]["status"]) == 0 and not bool(res[1]["unchanged"])                           # rank 1 saw rank 0's publication and stepped
