@@ -132,8 +132,13 @@ void talos_attention_launch(talos_ctx* ctx, HeadView q1, HeadView q2, HeadView k
 // to `sc` (the caller's probs buffer, or scratch), softmax in place, out = P.V as a second batched GEMM.  The scores
 // make one round trip through HBM (~4 S^2 x 4 bytes per head), which at S = 128 still costs a tenth of the fused
 // CUDA-core kernel's arithmetic time.  Returns false when the tensor-core GEMM does not take the shape.
+bool talos_attention_tc_fused(talos_ctx* ctx, const float* q, const float* k, const float* v, float* out, float* probs, int64_t BH,
+                              int64_t S, int64_t dqk, int64_t dv, float scale, int causal);
+
 static bool attention_fwd_tc(talos_ctx* ctx, const float* q, const float* k, const float* v, float* out, float* probs,
                              int64_t BH, int64_t S, int64_t dqk, int64_t dv, float scale, int causal, int mode) {
+  // fast mode, S <= 128: one fused kernel with the scores in tensor memory (attention_tc.cu)
+  if (mode == TALOS_MODE_TF32 && talos_attention_tc_fused(ctx, q, k, v, out, probs, BH, S, dqk, dv, scale, causal)) return true;
   if (S > 1024) return false;                                       // row softmax limit
   float* sc = probs ? probs : (float*)talos_workspace2(ctx, sizeof(float) * (size_t)(BH * S * S));
   const EpiArgs none = talos_epi_args(nullptr);

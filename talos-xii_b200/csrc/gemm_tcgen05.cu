@@ -571,6 +571,14 @@ static bool tc_ready(talos_ctx* ctx) {
   return ctx->tc_state > 0;
 }
 
+// For the other tensor-core kernels of the library (the fused attention): the same tensor maps and the same start-up check.
+bool talos_tc_make_operand_map(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool mn_major,
+                               int64_t batch, int64_t stride) { return make_tmap(out, base, rows, cols, ld, box_rows, mn_major, batch, stride); }
+bool talos_tc_make_output_map(CUtensorMap* out, const float* base, int64_t slabs, int64_t rows, int64_t cols, int64_t ld, int64_t slab_stride) {
+  return make_out_tmap(out, base, slabs, rows, cols, ld, slab_stride);
+}
+bool talos_tc_ready_for(talos_ctx* ctx) { return tc_ready(ctx); }
+
 bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                           const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcExtra* extra) {
   if (extra && extra->splits_out) *extra->splits_out = 1;
