@@ -424,6 +424,10 @@ struct MultiHeadLatentAttention {                                               
     Tensor att = attention(q_c, q_rot, k_c, k_rot, v_c, B, S, H, dh, dr);
     return w_o.forward(att);
   }
+  // forward_inference (:562-685): graph-free forward of ONE whole sequence [seq, dim], token-position RoPE, every token
+  // attending to every token -- which is what the cached variant below computes when it is handed the whole sequence
+  // and an empty cache.
+  std::vector<double> forward_inference(const std::vector<double>& xin) const { KVCache fresh(config.num_heads); return forward_inference_cached(xin, fresh, 0); }
   // forward_inference_cached (:688-841): `x` holds one or a few tokens of ONE sequence; token-position RoPE;
   // K/V rows are appended to the cache and the new tokens attend to every cached row.
   std::vector<double> forward_inference_cached(const std::vector<double>& xin, KVCache& cache, size_t start_pos) const {
@@ -495,6 +499,13 @@ struct LuckTransformer : Module {                                               
     Tensor out = Tensor::zeros({x.shape[0], x.shape[2]});
     check(talos_last_token(ctx(), x.d(), out.d(), (int64_t)x.shape[0], (int64_t)x.shape[1], (int64_t)x.shape[2]));
     return out;
+  }
+  std::vector<double> forward_inference(const std::vector<double>& x) const {       // :111-144: one whole sequence, graph-free
+    KVCache fresh(mla_layer.config.num_heads); return forward_inference_step(x, fresh, 0);
+  }
+  std::vector<double> last_token_inference(const std::vector<double>& x) const {    // :146-150
+    const size_t dim = out_proj.out_features, start = x.size() > dim ? x.size() - dim : 0;
+    return std::vector<double>(x.begin() + start, x.end());
   }
   std::vector<double> forward_inference_step(const std::vector<double>& x, KVCache& cache, size_t start_pos) const {   // :152-193
     auto add = [](std::vector<double> a, const std::vector<double>& b) { for (size_t i = 0; i < a.size(); ++i) a[i] += b[i]; return a; };

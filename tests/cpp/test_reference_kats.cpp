@@ -140,6 +140,17 @@ int main(int argc, char** argv) {
     EXPECT(diff < 1e-6);
     policy.backbone.mla_layer.prune_kv_cache(kv, 4); EXPECT(kv.len == 4);           // sliding window, src/transformer.rs:843-874
   });
+  run("transformer: graph-free whole-sequence forward_inference equals the tape path with token positions", [] {   // src/transformer.rs:111-150, :562-685
+    LuckTransformer t(8, 64, true, 99);
+    const size_t seq = 5;
+    Tensor x = Tensor::rand({1, seq, 8}, -0.5, 0.5, 17);
+    t.mla_layer.token_positions = true;                                   // the graph-free paths rotate by TOKEN position (:583-610)
+    const std::vector<double> tape = t.forward(x).to_vec(), flat = t.forward_inference(x.to_vec());
+    EXPECT(tape.size() == flat.size() && flat.size() == seq * 64);
+    double worst = 0; for (size_t i = 0; i < tape.size(); ++i) worst = std::max(worst, std::fabs(tape[i] - flat[i]));
+    EXPECT(worst < (mode() == TALOS_MODE_TF32 ? 5e-3 : 1e-5));           // two routes through the same arithmetic mode
+    EXPECT(t.last_token_inference(flat) == std::vector<double>(flat.end() - 64, flat.end()));
+  });
   run("ppo: advantage block (reward normalisation, GAE, advantage normalisation)", [] {   // src/ppo.rs:444-480, :650-675
     RunningMeanStd rn; for (double r : {1.0, 2.0, -1.0}) rn.update(r);
     EXPECT(std::fabs(rn.count - 3.0001) < 1e-12);
