@@ -230,15 +230,23 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   }
   p->t += 1;
   float* stat_slot = p->step_stats + 4 * (p->steps_in_epoch % MAX_STEPS_PER_EPOCH);
-  if (peer) {
+  // One kernel applies the step: sum of the ranks' gradient slots in rank order (over peer memory when there are peers;
+  // a single rank "sums" its own buffer), Adam, and the TF32-prepared copies of the new weights.  Only the NCCL route
+  // (peers that could not map each other's memory) needs the separate all-reduce + Adam + preparation launches.
+  const bool fused_update = peer || (!comm && p->n_int % 4 == 0);
+  if (fused_update) {
     XchgAdamArgs a{};
-    for (int r = 0; r < comm->nranks; ++r) { a.slot[r] = comm->x.slot(r, seq); a.peer_flags[r] = comm->x.flags(r); }
-    a.world = comm->nranks; a.rank = comm->rank; a.seq = seq; a.spins = comm->x.wait_spins; a.skip_signal = comm->x.dbg_skip_signal;
+    if (peer) {
+      for (int r = 0; r < comm->nranks; ++r) { a.slot[r] = comm->x.slot(r, seq); a.peer_flags[r] = comm->x.flags(r); }
+      a.world = comm->nranks; a.rank = comm->rank; a.seq = seq; a.spins = comm->x.wait_spins; a.skip_signal = comm->x.dbg_skip_signal;
+    } else {
+      a.slot[0] = G; a.peer_flags[0] = nullptr; a.world = 1; a.rank = 0; a.seq = 0; a.skip_signal = 1;     // nobody to signal, nobody to wait for
+    }
     a.status = ctx->dev_status; a.params = p->params; a.m = p->m; a.v = p->v; a.w_hi = p->w_hi; a.w_lo = p->w_lo; a.grads_out = p->grads; a.stats_out = stat_slot;
     a.n = p->n_int; a.lr = c.lr; a.b1 = c.beta1; a.b2 = c.beta2; a.eps = c.eps;
     a.inv_bc1 = (float)(1.0 / (1.0 - pow((double)c.beta1, (double)p->t))); a.inv_bc2 = (float)(1.0 / (1.0 - pow((double)c.beta2, (double)p->t)));
     talos_xchg_adam_launch(ctx, a);
-    comm->x.seq = seq; comm->x.dbg_skip_signal = 0;
+    if (peer) { comm->x.seq = seq; comm->x.dbg_skip_signal = 0; }
     p->weights_prepared = p->w_hi != nullptr;
   } else {
     if (comm) { if ((st = talos_comm_allreduce_sum(comm, G, p->n_int + 4))) throw talos_error(st, talos_last_error_string()); }
