@@ -342,6 +342,13 @@ def hbm_section(talos, ctx, timer, pk, pk_kind, local, reps=20):
     c = torch.empty(S * dr // 2, device="cuda"); sn = torch.empty_like(c); L.talos_rope_table(ctx.handle, dr, S, 10000.0, P(c), P(sn))
     xr = torch.randn(Bq, S, H, dr, device="cuda"); yr = torch.empty_like(xr)
     add("rope", [Bq, S, H, dr], 2.0 * xr.numel() * 4 / 1e9, lambda: L.talos_rope(ctx.handle, P(xr), P(yr), P(c), P(sn), c.numel(), Bq, S, H, dr, 0, 0, 0))
+    del xr, yr
+    n = 1 << 25                           # rollout buffer: GAE scan + advantage normalisation (src/ppo.rs:650-675)
+    rw = torch.randn(n, device="cuda"); vl = torch.randn(n, device="cuda"); tm = (torch.rand(n, device="cuda") < 0.02).to(torch.int32)
+    adv = torch.empty(n, device="cuda"); ret = torch.empty(n, device="cuda")
+    add("gae", [n], (2 * 12.0 + 8.0) * n / 1e9, lambda: L.talos_gae(ctx.handle, P(rw), P(vl), P(tm), n, 0.99, 0.95, 0.0, 1.0, P(adv), P(ret)))   # two passes read r, V, terminal; the second writes A and R
+    add("normalize_slice", [n], 16.0 * n / 1e9, lambda: L.talos_normalize_slice(ctx.handle, P(adv), n, P(ret), None))                          # three reads, one write
+    del rw, vl, tm, adv, ret
     BH, S, dqk, dv = 4096, 128, 96, 64    # config 4 attention core
     q = torch.randn(BH, S, dqk, device="cuda"); k = torch.randn_like(q); v = torch.randn(BH, S, dv, device="cuda"); o = torch.empty_like(v)
     att = []
