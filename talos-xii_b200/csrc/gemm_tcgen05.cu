@@ -14,6 +14,7 @@
 #include <cuda.h>
 
 #include <map>
+#include <unordered_map>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -284,36 +285,69 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are kept per thread, keyed on everything that goes into them: a training loop calls the same
+// products on the same buffers every step, and cuTensorMapEncodeTiled costs about a microsecond of host time per map
+// (three or four maps per product).  A map holds no reference to the memory it describes, so a stale entry for a
+// buffer that was freed and reallocated with the same address and shape is still the right map.
+struct TmapKey {
+  const void* base; int64_t a, b, c, d, e; int kind;
+  bool operator==(const TmapKey& o) const { return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d && e == o.e && kind == o.kind; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ULL;
+    for (int64_t v : {k.a, k.b, k.c, k.d, k.e, (int64_t)k.kind}) h = (h ^ (uint64_t)v) * 0x100000001B3ULL + (h >> 29);
+    return (size_t)h;
+  }
+};
+bool tmap_cached(const TmapKey& key, CUtensorMap* out, bool (*encode)(const TmapKey&, CUtensorMap*)) {
+  thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  if (!encode(key, out)) return false;
+  if (cache.size() >= 512) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
 // 3-D fp32 tensor map over `batch` row-major [rows][cols] matrices (cols contiguous) `stride` elements apart,
 // box = [1][box_rows][32 cols].  A plain GEMM is a batch of one.  Rows past the end of a batch member are filled
 // with zeros by the copy engine, never read from the next member.
-bool make_tmap(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool mn_major,
-               int64_t batch = 1, int64_t stride = 0) {
+bool encode_operand_map(const TmapKey& k, CUtensorMap* out) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
-  if (batch <= 1) { batch = 1; stride = rows * ld; }
+  const int64_t rows = k.a, cols = k.b, ld = k.c, batch = k.d, stride = k.e; const int box_rows = k.kind >> 1; const bool mn_major = k.kind & 1;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
   cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)stride * sizeof(float)};
   cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
   cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)k.base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+bool make_tmap(CUtensorMap* out, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, bool mn_major,
+               int64_t batch = 1, int64_t stride = 0) {
+  if (batch <= 1) { batch = 1; stride = rows * ld; }
+  return tmap_cached(TmapKey{base, rows, cols, ld, batch, stride, (box_rows << 1) | (mn_major ? 1 : 0)}, out, encode_operand_map);
 }
 
 // 3-D fp32 tensor map for results: [slabs][rows][cols], box = [1][32][32], 128B swizzle.  C itself is one
 // slab; split-K partial sums are `splits` dense slabs; a batched product has one slab per batch member,
 // `slab_stride` elements apart.  Stores are clipped per slab by the map.
-bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t rows, int64_t cols, int64_t ld, int64_t slab_stride) {
+bool encode_output_map(const TmapKey& k, CUtensorMap* out) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
+  const int64_t slabs = k.a, rows = k.b, cols = k.c, ld = k.d, slab_stride = k.e;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)slabs};
   cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)slab_stride * sizeof(float)};
   cuuint32_t box[3] = {32u, 32u, 1u};
   cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)k.base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t rows, int64_t cols, int64_t ld, int64_t slab_stride) {
+  return tmap_cached(TmapKey{base, slabs, rows, cols, ld, slab_stride, -1}, out, encode_output_map);
 }
 
 template <int BN, int STAGES, bool X3, int SBUF = 1>
