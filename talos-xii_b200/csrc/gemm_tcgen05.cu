@@ -155,53 +155,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t a_lbo = A_MN ? BK * 128 : 16, b_lbo = B_MN ? BK * 128 : 16;
       const uint32_t a_kstep = A_MN ? 1024 : UMMA_K * 4, b_kstep = B_MN ? 1024 : UMMA_K * 4;
       const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024, a_lay = A_MN ? 1 : 2, b_lay = B_MN ? 1 : 2;
-      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
+      int stage = 0; uint32_t phase = 0; int tcount = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true;
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
         const int ks = (it % per_batch) / tiles_mn;
         const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
-        if (!mbar_wait(tempty + acc, acc_phase[acc] ^ 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait((X3 ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
+        // The item's reduction runs as chains of chain_kb k-blocks (the whole item when chain_kb = 0): the first chain
+        // accumulates into the item's running buffer, every further one into the other buffer, which the epilogue warps
+        // fold into the running one -- the fp32-faithful mode keeps its accumulation chains short that way without
+        // sending partial tiles through memory.
+        const int run = tcount & 1; ++tcount;
+        const int ckb = g.chain_kb > 0 ? g.chain_kb : (kb1 - kb0);
+        for (int c0 = kb0; c0 < kb1 && ok; c0 += ckb) {
+          const int buf = (c0 == kb0) ? run : (run ^ 1), c1 = min(kb1, c0 + ckb);
+          if (!mbar_wait(tempty + buf, acc_phase[buf] ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          for (int kb = c0; kb < c1; ++kb) {
+            if (!mbar_wait((X3 ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
-            if (X3) {
-              const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
-              const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
-              tc_mma_tf32(d_tmem, dal, db, idesc, accum);      // lo.hi
-              tc_mma_tf32(d_tmem, da, dbl, idesc, 1u);         // hi.lo
-              tc_mma_tf32(d_tmem, da, db, idesc, 1u);          // hi.hi
-            } else {
-              tc_mma_tf32(d_tmem, da, db, idesc, accum);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint32_t accum = (kb > c0 || k > 0) ? 1u : 0u;
+              const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
+              if (X3) {
+                const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
+                const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
+                tc_mma_tf32(d_tmem, dal, db, idesc, accum);      // lo.hi
+                tc_mma_tf32(d_tmem, da, dbl, idesc, 1u);         // hi.lo
+                tc_mma_tf32(d_tmem, da, db, idesc, 1u);          // hi.hi
+              } else {
+                tc_mma_tf32(d_tmem, da, db, idesc, accum);
+              }
             }
+            tc_commit(empty + stage);                            // frees the stage when these MMAs retire
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          tc_commit(empty + stage);                            // frees the stage when these MMAs retire
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (!ok) break;
+          tc_commit(tfull + buf);                                // chain complete
+          acc_phase[buf] ^= 1;
         }
-        if (!ok) break;
-        tc_commit(tfull + acc);                                // accumulator complete
-        acc_phase[acc] ^= 1; acc ^= 1;
       }
     }
   } else if (warp < 2 + EPI_WARPS) {
     // ------------------------------------------------------------- epilogue: normally 8 warps, two per TMEM lane quadrant,
     // each taking half of the tile's columns (the epilogue is latency-bound per warp, so it needs the extra warps).
-    int acc = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
+    int tcount = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int bz = it / per_batch, r = it - bz * per_batch;
       const int ks = r / tiles_mn, rem = r % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
-      if (!mbar_wait(tfull + acc, acc_phase[acc], abort_flag)) { ok = false; break; }
+      const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
+      const int run = tcount & 1, other = run ^ 1; ++tcount;
+      const int ckb = g.chain_kb > 0 ? g.chain_kb : (kb1 - kb0);
+      const uint32_t t_run = tmem_base + (uint32_t)(run * BN), t_other = tmem_base + (uint32_t)(other * BN);
+      if (!mbar_wait(tfull + run, acc_phase[run], abort_flag)) { ok = false; break; }        // first chain: lands in the running buffer
       tc_fence_after();
-      tc_epilogue_tile<BN, EPI_WARPS, SBUF>(g, &tmap_c, tmem_base + (uint32_t)(acc * BN), warp, lane, stage_all + (warp - 2) * (32 * 32 * SBUF), (long long)mb * BM, nb, ks, bz, store_count);
+      for (int c0 = kb0 + ckb; c0 < kb1 && ok; c0 += ckb) {                                   // further chains: fold, hand the buffer back
+        if (!mbar_wait(tfull + other, acc_phase[other], abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        tc_fold_chain<BN, EPI_WARPS>(t_run, t_other, warp);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty + other);
+        acc_phase[other] ^= 1;
+      }
+      if (!ok) break;
+      tc_epilogue_tile<BN, EPI_WARPS, SBUF>(g, &tmap_c, t_run, warp, lane, stage_all + (warp - 2) * (32 * 32 * SBUF), (long long)mb * BM, nb, ks, bz, store_count);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty + acc);
-      acc_phase[acc] ^= 1; acc ^= 1;
+      if (lane == 0) mbar_arrive(tempty + run);
+      acc_phase[run] ^= 1;
     }
     if (lane == 0) tma_store_wait_read<0>();                 // shared memory must outlive the stores that read it
     __syncwarp();
@@ -374,6 +397,7 @@ void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, c
 }
 
 static inline bool x3_mode(int mode) { return mode == TALOS_MODE_TF32X3; }
+thread_local bool g_check_fold = false;   // set by the self-check: the whole reduction in one item, so that its 17 k-blocks are two chains folded on chip
 thread_local bool g_check_pair = false;   // set by the start-up self-check so that its short reduction still exercises the pair kernel
 
 // A batched product: `batch` independent GEMMs whose operands are `stride*` elements apart (batch 1: a plain GEMM).
@@ -426,6 +450,10 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // the cheapest r * (k-blocks per item + a few k-blocks' worth of per-item pipeline fill and epilogue) wins -- e.g. the
   // 256 x 256 x 65 536 weight gradient runs 2 x 147 items of 14 k-blocks on 148 CTAs instead of 2 x 128 of 16.
   const int cap = (x3 && !batched) ? 512 / BK : g.kb_total;     // (batched products with K > 512 are not routed here)
+  // The one-CTA kernel, too, meets the chain cap on chip (a finished chain is folded into a running sum in the second
+  // TMEM buffer), so an item may hold several chains: the 256 x 256 x 65 536 weight gradient then runs 2 x 74 items of 28
+  // k-blocks (two chains) instead of 2 x 147 of 14, which halves the partial tiles the gather kernel has to add.
+  const bool fold_one = x3 && !batched && !pair && !getenv("TALOS_TC_NO_FOLD");
   g.kb_per_split = g.kb_total;
   if (!batched && ((tiles * 2 <= workers && g.kb_total >= 16) || g.kb_total > cap)) {
     const int item_overhead = 3;
@@ -435,13 +463,15 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
       int kps = (int)ceil_div(g.kb_total, s_r);
       if (kps < 8 && r > 1) break;                                  // items would become shorter than their own overhead
       kps = std::max(kps, std::min(8, g.kb_total));
-      if (kps > cap) continue;
-      const long long cost = (long long)ceil_div((int64_t)tiles * ceil_div(g.kb_total, kps), workers) * (kps + item_overhead);
+      if (kps > cap && !(fold_one && kps <= 8 * cap)) continue;
+      const int chains = (int)ceil_div(kps, cap);
+      const long long cost = (long long)ceil_div((int64_t)tiles * ceil_div(g.kb_total, kps), workers) * (kps + item_overhead + (chains - 1));
       if (best_cost < 0 || cost < best_cost) { best_cost = cost; g.kb_per_split = kps; }
     }
-    if (g.kb_per_split > cap) g.kb_per_split = cap;
+    if (g.kb_per_split > cap && !(fold_one && best_cost >= 0)) g.kb_per_split = cap;
   }
-  g.chain_kb = 0;
+  if (g_check_fold && fold_one && g.kb_total > cap) g.kb_per_split = g.kb_total;
+  g.chain_kb = (fold_one && g.kb_per_split > cap) ? cap : 0;
   if (pair && x3 && g.kb_total > cap && !getenv("TALOS_TC_NO_FOLD")) {
     // CTA-pair kernel: the chain cap is met ON CHIP (finished chains are folded into a running sum in TMEM), so K is
     // split through memory only as far as it takes to keep the pairs busy: the smallest power-of-two split whose
@@ -585,6 +615,9 @@ bool self_check_shape(talos_ctx* ctx, const int M, const int N = 328, const int 
 // of three small ragged products (tiles must neither read nor write across batch members).
 bool self_check(talos_ctx* ctx) {
   bool ok = self_check_shape(ctx, 200) && self_check_shape(ctx, 72, 88, 104, 3);
+  g_check_fold = true;
+  ok = ok && self_check_shape(ctx, 200, 328, 520);                               // K = 520 in one item on the one-CTA kernel: two chains, folded on chip
+  g_check_fold = false;
   g_check_pair = true;
   ok = ok && self_check_shape(ctx, 456) && self_check_shape(ctx, 456, 328, 520);   // K = 520: two chains, folded on chip in 3xTF32 mode
   g_check_pair = false;

@@ -238,10 +238,10 @@ __device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restri
 // (round to nearest), for this warp's TMEM lane quadrant and column half.  This is how the fp32-faithful mode keeps its
 // accumulation chains short (the tensor core truncates when it adds into the accumulator) without sending partial
 // tiles through memory.
-template <int BN>
+template <int BN, int EPI_WARPS = 8>
 __device__ __forceinline__ void tc_fold_chain(uint32_t t_run, uint32_t t_acc, int warp) {
-  const int quad = warp & 3, half = (warp - 2) >> 2;
-  constexpr int HALF_COLS = BN >= 64 ? BN / 2 : BN;
+  const int quad = warp & 3, half = EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;
+  constexpr int HALF_COLS = (EPI_WARPS == 8 && BN >= 64) ? BN / 2 : BN;
   const uint32_t row = (uint32_t)(quad * 32) << 16;
 #pragma unroll 1
   for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 16) {
@@ -311,6 +311,31 @@ if (fuse && c < groups) {                                                       
   r[4 * c + 3] = __float_as_uint(v.w);                                                                              \
 }                                                                                                                   \
   }
+        // The common forward epilogue (bias and / or activation on a full 32-column chunk, nothing read per element)
+        // runs WITHOUT per-group conditions on every lane -- rows past M hold garbage the TMA store clips anyway -- so
+        // the 32 independent activation chains of a lane can be interleaved instead of running four at a time between
+        // branches.
+        const bool straight = g.splits == 1 && groups == 8 && !dact && !g.epi.beta && (g.epi.act || g.epi.bias);
+#define TALOS_EPI_STRAIGHT(A, HAS_BIAS)                                                                                 \
+  { const float4* bp = (const float4*)(g.epi.bias + n0);                                                                \
+    _Pragma("unroll") for (int c = 0; c < 8; ++c) {                                                                    \
+      const float4 b4 = HAS_BIAS ? __ldg(bp + c) : make_float4(0.f, 0.f, 0.f, 0.f);                                     \
+      r[4 * c] = __float_as_uint(talos_act(__uint_as_float(r[4 * c]) + b4.x, A));                                       \
+      r[4 * c + 1] = __float_as_uint(talos_act(__uint_as_float(r[4 * c + 1]) + b4.y, A));                               \
+      r[4 * c + 2] = __float_as_uint(talos_act(__uint_as_float(r[4 * c + 2]) + b4.z, A));                               \
+      r[4 * c + 3] = __float_as_uint(talos_act(__uint_as_float(r[4 * c + 3]) + b4.w, A));                               \
+    } }
+        if (straight) {
+          switch (g.epi.act * 2 + (g.epi.bias ? 1 : 0)) {
+            case 2: TALOS_EPI_STRAIGHT(1, false) break;
+            case 3: TALOS_EPI_STRAIGHT(1, true) break;
+            case 4: TALOS_EPI_STRAIGHT(2, false) break;
+            case 5: TALOS_EPI_STRAIGHT(2, true) break;
+            case 6: TALOS_EPI_STRAIGHT(3, false) break;
+            case 7: TALOS_EPI_STRAIGHT(3, true) break;
+            default: TALOS_EPI_STRAIGHT(0, true) break;
+          }
+        } else
         switch (fuse ? g.epi.act * 4 + dact : 0) {
           case 1: TALOS_EPI_MATH(0, 1) break;
           case 2: TALOS_EPI_MATH(0, 2) break;
@@ -321,6 +346,7 @@ if (fuse && c < groups) {                                                       
           default: if (g.epi.bias || g.epi.beta) { TALOS_EPI_MATH(0, 0) } break;
         }
 #undef TALOS_EPI_MATH
+#undef TALOS_EPI_STRAIGHT
       }
       if (store_count >= SBUF) { if (lane == 0) tma_store_wait_read<SBUF - 1>(); __syncwarp(); }
 #pragma unroll
