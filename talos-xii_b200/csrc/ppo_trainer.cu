@@ -1,5 +1,6 @@
 // Data-parallel PPO actor-critic update: the optimisation loops of PPO::update (src/ppo.rs:680-769)
 // for an MLP actor-critic, one fused sequence of GEMM / loss / Adam launches per minibatch.
+#include <functional>
 #include <vector>
 
 #include "comm.cuh"
@@ -262,7 +263,7 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
 // still being copied in on another stream).
 void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actions, const float* old_logp, const float* adv,
             const float* ret, int64_t N, int32_t epochs, float kl_stop, float* epoch_kl, int32_t* epochs_run,
-            const std::vector<cudaEvent_t>* ready = nullptr) {
+            const std::vector<cudaEvent_t>* ready = nullptr, const std::function<void(int64_t)>* stage_chunk = nullptr) {
   const int64_t mb = p->cfg.minibatch;
   int32_t done = 0;
   std::vector<float> stats;
@@ -285,6 +286,7 @@ void update(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* act
       int64_t n = std::min(mb, N - s);
       if (ready && e == 0) TALOS_CHECK_CUDA(cudaStreamWaitEvent(p->ctx->stream, (*ready)[(size_t)(s / mb)], 0));
       step(p, comm, obs + s * p->cfg.obs_dim, actions + s, old_logp + s, adv + s, ret + s, n);
+      if (stage_chunk && e == 0) (*stage_chunk)(s / mb + 2);           // keep the copy stream two minibatches ahead of the steps
     }
     done = e + 1;
     if (defer) continue;
@@ -487,7 +489,11 @@ TALOS_API talos_status talos_ppo_update_host(talos_ppo* p, talos_comm* comm, con
   cudaStream_t cs = p->copy_stream;
   TALOS_CHECK_CUDA(cudaEventRecord(p->staging_free, p->ctx->stream));        // earlier work may still read the staging buffer
   TALOS_CHECK_CUDA(cudaStreamWaitEvent(cs, p->staging_free, 0));
-  for (int64_t c = 0; c < chunks; ++c) {
+  // The copies of minibatch c are enqueued when step c - 2 has been launched (the first two up front), not all at the
+  // start: enqueueing 5 copies per minibatch for the whole shard first would hold back the first step's launch by the
+  // host time of all of them.
+  const std::function<void(int64_t)> stage_chunk = [&](int64_t c) {
+    if (c >= chunks) return;
     const int64_t s0 = c * mb, n = std::min(mb, N - s0);
     TALOS_CHECK_CUDA(cudaMemcpyAsync(obs + s0 * O, obs_h + s0 * O, sizeof(float) * (size_t)(n * O), cudaMemcpyHostToDevice, cs));
     TALOS_CHECK_CUDA(cudaMemcpyAsync(actions + s0, actions_h + s0, sizeof(int32_t) * (size_t)n, cudaMemcpyHostToDevice, cs));
@@ -495,8 +501,10 @@ TALOS_API talos_status talos_ppo_update_host(talos_ppo* p, talos_comm* comm, con
     TALOS_CHECK_CUDA(cudaMemcpyAsync(adv + s0, adv_h + s0, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, cs));
     TALOS_CHECK_CUDA(cudaMemcpyAsync(ret + s0, ret_h + s0, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, cs));
     TALOS_CHECK_CUDA(cudaEventRecord(p->chunk_ready[(size_t)c], cs));
-  }
-  update(p, comm, obs, actions, old_logp, adv, ret, N, epochs, kl_stop, epoch_kl_host, epochs_run_out, &p->chunk_ready);
+  };
+  stage_chunk(0); stage_chunk(1);
+  if (epochs == 0) for (int64_t c = 2; c < chunks; ++c) stage_chunk(c);       // (no steps to ride on: nothing to do, but leave the buffers consistent)
+  update(p, comm, obs, actions, old_logp, adv, ret, N, epochs, kl_stop, epoch_kl_host, epochs_run_out, &p->chunk_ready, &stage_chunk);
   TALOS_ENTRY_END
 }
 
