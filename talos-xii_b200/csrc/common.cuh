@@ -159,6 +159,10 @@ int talos_colsum_partials_launch(talos_ctx* ctx, const float* dy, float* dz, con
 struct TcExtra {
   const float* b_hi = nullptr; const float* b_lo = nullptr;
   float* partial = nullptr; size_t partial_floats = 0; int* splits_out = nullptr;
+  // Fused hidden-layer input gradient: C = (A.B^T) * (1 - tanh_saved^2) and per-slab column sums of C into colsum_part
+  // ([*colsum_slabs_out][N], summed by the caller).  *colsum_slabs_out stays 0 when the launch did not take the fused
+  // route: C is then the plain product and the caller applies the factor itself.
+  const float* tanh_saved = nullptr; int64_t ld_saved = 0; float* colsum_part = nullptr; size_t colsum_floats = 0; int* colsum_slabs_out = nullptr;
 };
 bool talos_gemm_tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                           const float* B, int64_t ldb, float* C, int64_t ldc, int mode, const EpiArgs& epi, const TcExtra* extra = nullptr);

@@ -43,10 +43,11 @@ template <bool X3, bool BPS> struct TcRoles {
 };
 
 // SBUF: staging buffers per epilogue warp (2 where the configuration leaves the shared memory for it).
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
-__global__ void __launch_bounds__((TcRoles<X3, BPS>::THREADS), MINB)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, TcArgs g) {
+// AUXT: the epilogue multiplies by tanh'(saved activation), fetching the activation tiles by TMA (tmap_aux), and
+// accumulates the column sums of what it stores (see tc_epilogue_tile_aux).
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB, bool BPS, int SBUF, bool AUXT>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, const CUtensorMap& tmap_b_lo,
+                                             const CUtensorMap* tmap_aux, const TcArgs& g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
   constexpr int EPI_WARPS = TcRoles<X3, BPS>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS>::CONV_WARPS;
@@ -58,6 +59,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* sBlo = sAlo + (X3 ? STAGES * A_BYTES : 0);
   float* stage_all = (float*)(sBlo + (X3 ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
   uint64_t* bars = (uint64_t*)(stage_all + 8 * 32 * 32 * SBUF);
+  uint64_t* aux_bars = bars; bars += AUXT ? 8 : 0;                   // AUXT: one barrier per epilogue warp for its activation tiles
   uint64_t* full = bars;                   // TMA -> (converter | issuer)
   uint64_t* conv = full + STAGES;          // converter -> issuer (X3)
   uint64_t* empty = conv + STAGES;         // issuer (commit) -> TMA
@@ -70,6 +72,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, CONV_WARPS ? CONV_WARPS : 1); mbar_init(empty + s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, EPI_WARPS); }
+    if (AUXT) for (int w = 0; w < 8; ++w) mbar_init(aux_bars + w, 1);
     abort_flag[0] = 0; abort_flag[1] = (int)g.wait_spins;
     fence_barrier_init();
   }
@@ -201,6 +204,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------- epilogue: normally 8 warps, two per TMEM lane quadrant,
     // each taking half of the tile's columns (the epilogue is latency-bound per warp, so it needs the extra warps).
     int tcount = 0; uint32_t acc_phase[2] = {0, 0}; bool ok = true; uint32_t store_count = 0;
+    TcAuxState aux_st{0u, {0.f, 0.f, 0.f, 0.f}};
+    float* const my_stage = stage_all + (warp - 2) * (32 * 32 * SBUF); uint64_t* const aux_bar = aux_bars + (warp - 2);
+    if (AUXT && (int)blockIdx.x < items && lane == 0) {        // the first chunk's saved-activation tile, into the first staging buffer
+      int mb0, nb0; tc_tile_coords((int)blockIdx.x % tiles_mn, g.m_tiles, g.n_tiles, g.group_m, mb0, nb0);
+      tc_aux_request(tmap_aux, my_stage, aux_bar, nb0 * BN + ((warp - 2) >> 2) * (BN / 2), (long long)mb0 * BM + (warp & 3) * 32);
+    }
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int bz = it / per_batch, r = it - bz * per_batch;
       const int ks = r / tiles_mn, rem = r % tiles_mn; int mb, nb; tc_tile_coords(rem, g.m_tiles, g.n_tiles, g.group_m, mb, nb);
@@ -220,7 +229,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         acc_phase[other] ^= 1;
       }
       if (!ok) break;
-      tc_epilogue_tile<BN, EPI_WARPS, SBUF>(g, &tmap_c, t_run, warp, lane, stage_all + (warp - 2) * (32 * 32 * SBUF), (long long)mb * BM, nb, ks, bz, store_count);
+      if (AUXT) {
+        const int nit = it + (int)gridDim.x; int nmb = 0, nnb = 0;
+        if (nit < items) tc_tile_coords(nit % tiles_mn, g.m_tiles, g.n_tiles, g.group_m, nmb, nnb);
+        if (!tc_epilogue_tile_aux<BN, SBUF>(g, &tmap_c, tmap_aux, t_run, warp, lane, my_stage, aux_bar, abort_flag,
+                                            (long long)mb * BM, nb, nit < items, (long long)nmb * BM, nnb, store_count, aux_st)) { ok = false; break; }
+      } else {
+        tc_epilogue_tile<BN, EPI_WARPS, SBUF>(g, &tmap_c, t_run, warp, lane, my_stage, (long long)mb * BM, nb, ks, bz, store_count);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + run);
@@ -228,6 +244,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (lane == 0) tma_store_wait_read<0>();                 // shared memory must outlive the stores that read it
     __syncwarp();
+    if (AUXT && g.colsum_part) {
+      // this warp's column sums over all the tiles of the CTA: one partial row per (CTA, lane quadrant); a warp owns
+      // half of the columns of each panel, zero where it had no tile
+      float* row = g.colsum_part + ((size_t)blockIdx.x * 4 + (warp & 3)) * g.N;
+      const int half = (warp - 2) >> 2; constexpr int CHUNKS = BN / 64;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {                            // j = (column panel) * CHUNKS + (32-column chunk of this warp's half)
+        const int col = (j / CHUNKS) * BN + half * (BN / 2) + (j % CHUNKS) * 32 + lane;
+        if ((j / CHUNKS) < g.n_tiles && col < g.N) row[col] = aux_st.acc[j];
+      }
+    }
   } else if (X3) {
     // ------------------------------------------------------------- converter warps: fp32 -> (hi, lo) TF32 pair
     constexpr int CONV_THREADS = (CONV_WARPS ? CONV_WARPS : 1) * 32;
@@ -269,6 +296,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
   }
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
+__global__ void __launch_bounds__((TcRoles<X3, BPS>::THREADS), MINB)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ TcArgs g) {
+  gemm_tc_body<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF, false>(tmap_a, tmap_b, tmap_c, tmap_b_lo, nullptr, g);
+}
+// The fused input-gradient configurations (3xTF32, prepared weights, both operands K-major): one more tensor map.
+template <int BN, int SBUF>
+__global__ void __launch_bounds__((TcRoles<true, true>::THREADS), 1)
+gemm_tc_aux_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
+                   const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ CUtensorMap tmap_aux, const __grid_constant__ TcArgs g) {
+  gemm_tc_body<BN, 2, true, false, false, 1, true, SBUF, true>(tmap_a, tmap_b, tmap_c, tmap_b_lo, &tmap_aux, g);
 }
 
 // Dense copy of a [rows][cols] matrix (pitch ld) rounded to TF32 with round-to-nearest.  In the fast TF32
@@ -536,13 +577,38 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   else if (!(((uintptr_t)C) & 15) && !(ldc & 3) && !(N & 3) && !(batched && (bt.stride_c & 3)) && !epi.aux_out && !both && epi_aligned) {
     g.tma_out = 1; ok = ok && make_out_tmap(&tc, C, g.batch, M, N, ldc, batched ? bt.stride_c : M * ldc);
   }
+  if (extra && extra->colsum_slabs_out) *extra->colsum_slabs_out = 0;
+  g.colsum_part = nullptr;
+  int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count);
+  // The input gradient of a tanh layer takes tanh' and the bias gradient's column sums into its epilogue: the K <= 64
+  // configuration (128-column tiles, two staging buffers) and the 256-column one (a single staging buffer).
+  const bool aux_cfg = presplit && !a_mn && !b_mn && !pair && splits == 1 && (short_k || bn == 256) && g.n_tiles * (bn / 64) <= 4;
+  const bool auxt = extra && extra->tanh_saved && extra->colsum_part && extra->colsum_slabs_out && aux_cfg && !(N & 31) && plain_epi && g.tma_out &&
+                    !(((uintptr_t)extra->tanh_saved) & 15) && !(extra->ld_saved & 3) && extra->colsum_floats >= (size_t)4 * grid * N &&
+                    !getenv("TALOS_TC_NO_FUSED_DACT");
+  CUtensorMap tx = tc;
+  if (auxt) ok = ok && make_out_tmap(&tx, extra->tanh_saved, 1, M, N, extra->ld_saved, M * extra->ld_saved);
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  if (auxt) {
+    g.colsum_part = extra->colsum_part;
+    if (bn == 128) {
+      const size_t smem = tc_smem_bytes<128, 2, true, 2>() + 64;
+      TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      gemm_tc_aux_kernel<128, 2><<<grid, TcRoles<true, true>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g);
+    } else {
+      const size_t smem = tc_smem_bytes<256, 2, true, 1>() + 64;
+      TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      gemm_tc_aux_kernel<256, 1><<<grid, TcRoles<true, true>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g);
+    }
+    talos_launched(ctx, "gemm_tcgen05");
+    *extra->colsum_slabs_out = 4 * grid;
+    return;
+  }
   if (pair) {
     talos_gemm_tc2_launch(ctx, a_mn, b_mn, x3, presplit, ta, tb, tc, tbl, g, 2 * std::min(tiles * splits, workers));
     if (splits > 1 && !keep_partials) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);
     return;
   }
-  int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count);
   // (tile width, stages and staging buffers per epilogue warp in TF32 mode, the same for the 3xTF32 kernels)
 #define TALOS_TC_CASE(BNv, ST, SB, ST3, SB3)                                                                      \
   if (bn == BNv) {                                                                                                \

@@ -206,6 +206,17 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   // gradient's column sums at the same time.
   auto backprop_hidden = [&](int i, const float* dz_next, int64_t k, int64_t w_off, float* dh, const float* h_saved, float* db, float* part) {
     if (H % 4 == 0 && H <= 1024) {                                              // what the streaming kernel takes (buffers are aligned)
+      // Short reductions (the heads' K = 32) take the factor and the column sums into the GEMM's own epilogue, which
+      // fetches the saved activation tiles by TMA: no streaming pass at all.
+      if (p->partials && p->w_hi && p->cfg.mode == TALOS_MODE_TF32X3) {
+        int slabs = 0;
+        TcExtra x; x.b_hi = p->w_hi + w_off; x.b_lo = p->w_lo ? p->w_lo + w_off : nullptr;
+        x.tanh_saved = h_saved; x.ld_saved = H; x.colsum_part = part; x.colsum_floats = (size_t)p->cap_b; x.colsum_slabs_out = &slabs;
+        if (talos_gemm_tc_launch(ctx, 0, 1, n, H, k, dz_next, k, p->params + w_off, k, dh, H, p->cfg.mode, none, &x)) {
+          if (slabs > 0) seg(i, db, part, H, slabs); else bias_grad(i, dh, h_saved, H, db, part);
+          return;
+        }
+      }
       gemm_w(p, 0, 1, n, H, k, dz_next, k, w_off, k, dh, H, none);
       bias_grad(i, dh, h_saved, H, db, part);
       return;

@@ -18,6 +18,7 @@ struct TcArgs {
   int chain_kb;                            // CTA-pair 3xTF32 kernel: k-blocks per accumulation chain folded on chip (0: one chain per item)
   int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
   long long stride_c;                      // elements between consecutive batch members of C
+  float* colsum_part;                      // AUXT kernels: [4 * grid][N] per-warp-quadrant column sums of the stored result (bias gradient)
   int group_m;                             // tile order: m-tiles are walked in groups of this many per column sweep (L2 reuse); >= m_tiles: plain order
   unsigned wait_spins;                     // poll limit of every bounded wait (WAIT_SPINS unless a test shortened it)
   int dbg_skip_kb;                         // test hook: CTA 0's producer never loads this k-block of its first item (-1: off)
@@ -385,6 +386,99 @@ if (fuse && c < groups) {                                                       
       __syncwarp();
     }
   }
+}
+
+
+// Column sums of a 32 x 32 chunk held one row per lane (r[j] = column j of this lane's row): after five exchange rounds
+// lane j holds the sum of column j over the 32 rows.  Each round halves the values a lane keeps: it gives the half that
+// belongs to its partner's columns and adds the partner's contribution to its own half (31 shuffles in all).
+__device__ __forceinline__ float tc_chunk_colsum(const uint32_t (&r)[32], int lane) {
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float lo = __uint_as_float(r[i]), hi = __uint_as_float(r[i + 16]);
+    const bool up = lane & 16;
+    const float keep = up ? hi : lo, send = up ? lo : hi;
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int w = 8; w >= 1; w >>= 1) {
+#pragma unroll
+    for (int i = 0; i < w; ++i) {
+      const bool up = lane & w;
+      const float keep = up ? v[i + w] : v[i], send = up ? v[i] : v[i + w];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+    }
+  }
+  return v[0];
+}
+
+// Epilogue of the hidden-layer input gradient, fused: result = accumulator * (1 - h^2), and the column sums of the
+// result (the bias gradient) accumulated in registers across all the tiles of the CTA.  The saved activation tile h is
+// fetched by TMA INTO the staging buffer the result will leave from -- same 32 x 32 swizzled layout, so every lane
+// replaces its own row in place -- and is requested one chunk ahead, as soon as the store that last read that buffer
+// has let go of it.  State that lives across tiles is in `st`; a warp's chunks map onto st.acc[] as
+// (column panel) * (chunks per half tile) + chunk, which the launcher keeps within four.
+struct TcAuxState { uint32_t phase; float acc[4]; };
+template <int SBUF>
+__device__ __forceinline__ float* tc_stage_buf(float* stage, uint32_t count) { return stage + (SBUF == 2 ? (count & 1u) * (32 * 32) : 0); }
+__device__ __forceinline__ void tc_aux_request(const CUtensorMap* tmap_aux, float* buf, uint64_t* aux_bar, int n0, long long m0) {
+  mbar_expect_tx(aux_bar, 32 * 32 * 4);
+  tma_load_3d(buf, tmap_aux, n0, (int)m0, 0, aux_bar);
+}
+template <int BN, int SBUF>
+__device__ __forceinline__ bool tc_epilogue_tile_aux(const TcArgs& g, const CUtensorMap* tmap_c, const CUtensorMap* tmap_aux, uint32_t t_base, int warp, int lane,
+                                                     float* stage, uint64_t* aux_bar, volatile int* abort_flag, long long m_base, int nb,
+                                                     bool next_valid, long long next_m_base, int next_nb, uint32_t& store_count, TcAuxState& st) {
+  const int quad = warp & 3, half = (warp - 2) >> 2;
+  const long long m0 = m_base + quad * 32;
+  const uint32_t t_row = t_base + ((uint32_t)(quad * 32) << 16);
+  const int rows_valid = (int)max(0LL, min((long long)32, (long long)g.M - m0));
+  constexpr int HALF_COLS = BN / 2, CHUNKS = HALF_COLS / 32;
+  if (next_valid && lane < CHUNKS && next_m_base + quad * 32 < g.M)   // the next tile's activation chunks: into L2 while this tile is worked on
+    tma_prefetch_3d(tmap_aux, next_nb * BN + half * HALF_COLS + lane * 32, (int)(next_m_base + quad * 32), 0);
+#pragma unroll 1
+  for (int ci = 0; ci < CHUNKS; ++ci) {
+    const int c0 = half * HALF_COLS + ci * 32;
+    const int n0 = nb * BN + c0;
+    float* buf = tc_stage_buf<SBUF>(stage, store_count);
+    uint32_t r[32];
+    tmem_ld32(t_row + (uint32_t)c0, r);
+    tmem_ld_wait();
+    if (!mbar_wait(aux_bar, st.phase, abort_flag)) return false;
+    st.phase ^= 1;
+    const bool row_ok = lane < rows_valid;                     // rows past M hold the map's fill value; they must not reach the sums
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float4* cell = (float4*)(buf + lane * 32 + ((c ^ (lane & 7)) << 2));
+      const float4 a = *cell;
+      const float x0 = __uint_as_float(r[4 * c]) * (1.f - a.x * a.x), x1 = __uint_as_float(r[4 * c + 1]) * (1.f - a.y * a.y);
+      const float x2 = __uint_as_float(r[4 * c + 2]) * (1.f - a.z * a.z), x3 = __uint_as_float(r[4 * c + 3]) * (1.f - a.w * a.w);
+      const float4 x = make_float4(row_ok ? x0 : 0.f, row_ok ? x1 : 0.f, row_ok ? x2 : 0.f, row_ok ? x3 : 0.f);
+      *cell = x;
+      r[4 * c] = __float_as_uint(x.x); r[4 * c + 1] = __float_as_uint(x.y); r[4 * c + 2] = __float_as_uint(x.z); r[4 * c + 3] = __float_as_uint(x.w);
+    }
+    fence_proxy_async();
+    __syncwarp();
+    ++store_count;
+    if (lane == 0) {
+      if (rows_valid > 0) tma_store_3d(tmap_c, buf, n0, (int)m0, 0);       // (a row block wholly past M is only padding)
+      tma_store_commit();                                                  // one group per chunk, stored or not: the waits below count groups
+      const bool more = ci + 1 < CHUNKS;
+      if (more || next_valid) {
+        tma_store_wait_read<SBUF - 1>();                                   // the store that last read the next chunk's buffer
+        if (more) tc_aux_request(tmap_aux, tc_stage_buf<SBUF>(stage, store_count), aux_bar, n0 + 32, m0);
+        else tc_aux_request(tmap_aux, tc_stage_buf<SBUF>(stage, store_count), aux_bar, next_nb * BN + half * HALF_COLS, next_m_base + quad * 32);
+      }
+    }
+    {
+      const float cs = tc_chunk_colsum(r, lane);               // lane l: the sum of the chunk's column l
+      const int slot = (nb * CHUNKS + ci) & 3;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) st.acc[j] += (j == slot) ? cs : 0.f;
+    }
+  }
+  return true;
 }
 
 }  // namespace
