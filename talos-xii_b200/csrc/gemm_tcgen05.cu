@@ -174,21 +174,41 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
           for (int kb = c0; kb < c1; ++kb) {
-            if (!mbar_wait((X3 ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
+            // 3xTF32: the products that need no converted operand (hi.hi, and hi.lo when B arrives pre-split) are issued
+            // as soon as the loads have landed, beside the converter; the rest once the lo tiles are written.
+            const bool early = X3 && g.early_pass;
+            if (!mbar_wait((X3 && !early ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
+            const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
+            if (early) {
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint32_t accum = (kb > c0 || k > 0) ? 1u : 0u;
-              const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
-              if (X3) {
-                const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
-                const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
-                tc_mma_tf32(d_tmem, dal, db, idesc, accum);      // lo.hi
-                tc_mma_tf32(d_tmem, da, dbl, idesc, 1u);         // hi.lo
-                tc_mma_tf32(d_tmem, da, db, idesc, 1u);          // hi.hi
-              } else {
-                tc_mma_tf32(d_tmem, da, db, idesc, accum);
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
+                tc_mma_tf32(d_tmem, da, db, idesc, (kb > c0 || k > 0) ? 1u : 0u);                                  // hi.hi
+                if (BPS) tc_mma_tf32(d_tmem, da, make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay), idesc, 1u);    // hi.lo
+              }
+              if (!mbar_wait(conv + stage, phase, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
+                tc_mma_tf32(d_tmem, dal, db, idesc, 1u);                                                            // lo.hi
+                if (!BPS) tc_mma_tf32(d_tmem, make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay), idesc, 1u);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint32_t accum = (kb > c0 || k > 0) ? 1u : 0u;
+                const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
+                if (X3) {
+                  const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lay);
+                  tc_mma_tf32(d_tmem, dal, db, idesc, accum);      // lo.hi
+                  tc_mma_tf32(d_tmem, da, dbl, idesc, 1u);         // hi.lo
+                  tc_mma_tf32(d_tmem, da, db, idesc, 1u);          // hi.hi
+                } else {
+                  tc_mma_tf32(d_tmem, da, db, idesc, accum);
+                }
               }
             }
             tc_commit(empty + stage);                            // frees the stage when these MMAs retire
@@ -459,6 +479,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
+  g.early_pass = getenv("TALOS_TC_NO_EARLY") ? 0 : 1;
   g.wait_spins = ctx->dbg_wait_spins ? ctx->dbg_wait_spins : WAIT_SPINS; g.dbg_skip_kb = ctx->dbg_skip_kb;
   // Streamed K-major operands (more than 8 MB, i.e. not something that stays in L2 anyway) of the 3xTF32 kernels are
   // prefetched into L2 ahead of the loads: those kernels have only two or three stages in flight.  Measured on

@@ -19,6 +19,7 @@ struct TcArgs {
   int batch;                               // independent problems (third coordinate of every tensor map); 1 for a plain GEMM
   long long stride_c;                      // elements between consecutive batch members of C
   float* colsum_part;                      // AUXT kernels: [4 * grid][N] per-warp-quadrant column sums of the stored result (bias gradient)
+  int early_pass;                          // 3xTF32: issue the products of unconverted operands before the converter is done
   int group_m;                             // tile order: m-tiles are walked in groups of this many per column sweep (L2 reuse); >= m_tiles: plain order
   unsigned wait_spins;                     // poll limit of every bounded wait (WAIT_SPINS unless a test shortened it)
   int dbg_skip_kb;                         // test hook: CTA 0's producer never loads this k-block of its first item (-1: off)
