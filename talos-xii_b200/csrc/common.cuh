@@ -147,6 +147,14 @@ void talos_gemm_fp32_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t
 // Returns false when the shape/alignment is not eligible (caller falls back to the fp32 kernel).
 // First stage of the column sums only: dZ = dY * act'(saved) when dact != 0 (dz may alias dy) and the per-slab column
 // sums of dZ left in `partial` ([slabs][n]); returns the slab count, 0 (nothing launched) when the shape is not served.
+// The PPO loss kernel without its statistics pass: per-block {loss, kl} sums into partial[blocks][2] (returns blocks =
+// ceil(n / 128)) and, when colsum_part is given, per-block column sums of [dlogits | dvalue | 0...] into
+// colsum_part[blocks][cs_width] (only where talos_ppo_loss_colsum_supported says so).
+int talos_ppo_loss_launch(talos_ctx* ctx, const float* logits, int64_t ld_logits, const float* values, int64_t value_stride, const int32_t* actions,
+                          const float* old_logp, const float* adv, const float* ret, int64_t n, int32_t n_actions, float clip, float c_value,
+                          float c_entropy, float denom, float* dlogits, int64_t ld_out, float* dvalues, int64_t dvalue_stride, float* partial,
+                          float* colsum_part, int cs_width);
+bool talos_ppo_loss_colsum_supported(int32_t n_actions, int cs_width);
 int talos_colsum_partials_launch(talos_ctx* ctx, const float* dy, float* dz, const float* saved, int dact, int64_t rows, int64_t n,
                                  float* partial, int64_t cap);
 // Optional extras for callers that run the same products every step (the PPO trainer):

@@ -36,9 +36,11 @@ namespace {
 // Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, then the epilogue warps, then (3xTF32) the converter
 // warps.  When both operands are split in the kernel (no pre-split B: the weight-gradient products, whose epilogue
 // runs once per 16 k-blocks) the converter is the busy role, so it gets eight warps and the epilogue four.
-template <bool X3, bool BPS> struct TcRoles {
-  static constexpr int EPI_WARPS = (X3 && !BPS) ? 4 : 8;
-  static constexpr int CONV_WARPS = X3 ? (BPS ? 4 : 8) : 0;
+template <bool X3, bool BPS, int BN = 256> struct TcRoles {
+  // (narrow tiles with a pre-split B are converter-bound too: their epilogue moves 32 or 64 columns a tile)
+  static constexpr bool CONV_HEAVY = X3 && (!BPS || BN <= 64);
+  static constexpr int EPI_WARPS = CONV_HEAVY ? 4 : 8;
+  static constexpr int CONV_WARPS = X3 ? (CONV_HEAVY ? 8 : 4) : 0;
   static constexpr int THREADS = (2 + EPI_WARPS + CONV_WARPS) * 32;       // 448 (3xTF32) or 320 (TF32)
 };
 
@@ -50,7 +52,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
                                              const CUtensorMap* tmap_aux, const TcArgs& g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
   constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
-  constexpr int EPI_WARPS = TcRoles<X3, BPS>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS>::CONV_WARPS;
+  constexpr int EPI_WARPS = TcRoles<X3, BPS, BN>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS, BN>::CONV_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
@@ -319,7 +321,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
 }
 
 template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
-__global__ void __launch_bounds__((TcRoles<X3, BPS>::THREADS), MINB)
+__global__ void __launch_bounds__((TcRoles<X3, BPS, BN>::THREADS), MINB)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ TcArgs g) {
   gemm_tc_body<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF, false>(tmap_a, tmap_b, tmap_c, tmap_b_lo, nullptr, g);
@@ -444,7 +446,7 @@ void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, co
   auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF>;
   size_t smem = tc_smem_bytes<BN, STAGES, X3, SBUF>();
   TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, TcRoles<X3, BPS>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
+  kern<<<grid, TcRoles<X3, BPS, BN>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
   talos_launched(ctx, "gemm_tcgen05");
 }
 

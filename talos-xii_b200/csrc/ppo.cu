@@ -15,8 +15,15 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
                 const int* __restrict__ actions, const float* __restrict__ old_logp, const float* __restrict__ adv,
                 const float* __restrict__ ret, long long n, int n_actions, float clip, float c_v, float c_h, float inv_denom,
                 float* __restrict__ dlogits, long long ld_out, float* __restrict__ dvalues, long long dvs,
-                float* __restrict__ partial, int vec, int32_t* __restrict__ status) {
+                float* __restrict__ partial, int vec, int32_t* __restrict__ status, float* __restrict__ colsum_part, int cs_width) {
   __shared__ float sh_loss[128], sh_kl[128];
+  __shared__ float sh_cs[4][MAX_ACTIONS + 1];
+  const bool want_cs = colsum_part != nullptr;                 // block-uniform
+  const int na_cs = A > 0 ? A : n_actions;
+  float dv_out = 0.f;
+  float l_keep[A > 0 ? A : 1];                                 // this row's dlogits, for the column sums (specialised widths only)
+#pragma unroll
+  for (int a = 0; a < (A > 0 ? A : 1); ++a) l_keep[a] = 0.f;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   float loss = 0.f, kl = 0.f;
   if (i < n) {
@@ -80,12 +87,35 @@ ppo_loss_kernel(const float* __restrict__ logits, long long ld, const float* __r
         o.x = (l[a] - expf(q.x - lse) * sum_d) * inv_denom; o.y = (l[a + 1] - expf(q.y - lse) * sum_d) * inv_denom;
         o.z = (l[a + 2] - expf(q.z - lse) * sum_d) * inv_denom; o.w = (l[a + 3] - expf(q.w - lse) * sum_d) * inv_denom;
         *(float4*)(dlogits + i * ld_out + a) = o;
+        if (A > 0) { l_keep[a] = o.x; l_keep[a + 1] = o.y; l_keep[a + 2] = o.z; l_keep[a + 3] = o.w; }
       }
     } else {
 #pragma unroll
-      for (int a = 0; a < na; ++a) { float lp_p = expf(logits[i * ld + a] - lse); dlogits[i * ld_out + a] = (l[a] - lp_p * sum_d) * inv_denom; }
+      for (int a = 0; a < na; ++a) {
+        float lp_p = expf(logits[i * ld + a] - lse); const float o = (l[a] - lp_p * sum_d) * inv_denom;
+        dlogits[i * ld_out + a] = o;
+        if (A > 0) l_keep[a] = o;
+      }
     }
-    dvalues[i * dvs] = c_v * 2.f * dvl * inv_denom;
+    dv_out = c_v * 2.f * dvl * inv_denom;
+    dvalues[i * dvs] = dv_out;
+  }
+  if (A > 0 && want_cs) {
+    // Column sums of this block's rows of [dlogits | dvalue | zero padding] (the fused heads' bias gradient): warp
+    // shuffles per column, then the four warps' sums in warp order.
+    const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+#pragma unroll
+    for (int a = 0; a <= A; ++a) {
+      float v = a < A ? l_keep[a < A ? a : 0] : dv_out;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (ln == 0) sh_cs[w][a] = v;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < cs_width) {
+      const int a = threadIdx.x;
+      colsum_part[(size_t)blockIdx.x * cs_width + a] = a <= na_cs ? ((sh_cs[0][a] + sh_cs[1][a]) + (sh_cs[2][a] + sh_cs[3][a])) : 0.f;
+    }
   }
   sh_loss[threadIdx.x] = loss; sh_kl[threadIdx.x] = kl; __syncthreads();
   for (int o = 64; o > 0; o >>= 1) {
@@ -142,6 +172,23 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
 
 }  // namespace
 
+// The loss kernel alone: per-block {loss, kl} sums into partial[blocks][2] (blocks = ceil(n / 128), returned) and,
+// when colsum_part is given (widths the kernel is specialised for, the value gradient in column n_actions of the
+// same rows), per-block column sums of [dlogits | dvalue | 0...] into colsum_part[blocks][cs_width].
+int talos_ppo_loss_launch(talos_ctx* ctx, const float* logits, int64_t ld_logits, const float* values, int64_t value_stride, const int32_t* actions,
+                          const float* old_logp, const float* adv, const float* ret, int64_t n, int32_t n_actions, float clip, float c_value,
+                          float c_entropy, float denom, float* dlogits, int64_t ld_out, float* dvalues, int64_t dvalue_stride, float* partial,
+                          float* colsum_part, int cs_width) {
+  const int blocks = (int)ceil_div(n, 128);
+#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial, vec, ctx->dev_status, colsum_part, cs_width)
+  const int vec = (((uintptr_t)logits | (uintptr_t)dlogits) & 15) == 0 && ld_logits % 4 == 0 && ld_out % 4 == 0;
+  if (n_actions == 16) TALOS_PPO_LAUNCH(16); else if (n_actions == 5) TALOS_PPO_LAUNCH(5); else TALOS_PPO_LAUNCH(0);
+#undef TALOS_PPO_LAUNCH
+  talos_launched(ctx, "ppo_loss");
+  return blocks;
+}
+bool talos_ppo_loss_colsum_supported(int32_t n_actions, int cs_width) { return (n_actions == 16 || n_actions == 5) && cs_width > n_actions && cs_width <= 128; }
+
 TALOS_API talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logits, int64_t ld_logits, const float* values,
                                               int64_t value_stride, const int32_t* actions, const float* old_logp,
                                               const float* adv, const float* ret, int64_t n, int32_t n_actions, float clip,
@@ -155,11 +202,8 @@ TALOS_API talos_status talos_ppo_loss_fwd_bwd(talos_ctx* ctx, const float* logit
   TALOS_REQUIRE(logits && values && actions && old_logp && adv && ret && dlogits && dvalues && stats, TALOS_ERR_ARG, "null pointer");
   int blocks = (int)ceil_div(n, 128);
   float* partial = (float*)talos_workspace(ctx, sizeof(float) * 2 * (size_t)blocks);
-#define TALOS_PPO_LAUNCH(A) ppo_loss_kernel<A><<<blocks, 128, 0, ctx->stream>>>(logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, 1.f / denom, dlogits, ld_out, dvalues, dvalue_stride, partial, vec, ctx->dev_status)
-  const int vec = (((uintptr_t)logits | (uintptr_t)dlogits) & 15) == 0 && ld_logits % 4 == 0 && ld_out % 4 == 0;
-  if (n_actions == 16) TALOS_PPO_LAUNCH(16); else if (n_actions == 5) TALOS_PPO_LAUNCH(5); else TALOS_PPO_LAUNCH(0);
-#undef TALOS_PPO_LAUNCH
-  talos_launched(ctx, "ppo_loss");
+  talos_ppo_loss_launch(ctx, logits, ld_logits, values, value_stride, actions, old_logp, adv, ret, n, n_actions, clip, c_value, c_entropy, denom, dlogits,
+                        ld_out, dvalues, dvalue_stride, partial, nullptr, 0);
   ppo_stats_kernel<<<1, 256, 0, ctx->stream>>>(partial, blocks, (float)n, stats);
   talos_launched(ctx, "ppo_stats");
   TALOS_ENTRY_END

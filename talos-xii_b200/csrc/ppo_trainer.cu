@@ -23,6 +23,7 @@ struct talos_ppo {
   // The split-K partial results of the three weight-gradient products and the row-slab partial sums of the three
   // bias gradients stay here until ONE kernel reduces all six into the flat gradient buffer.
   float* partials = nullptr; int64_t cap_w2 = 0, cap_w1 = 0, cap_wh = 0, cap_b = 0;
+  float* loss_part = nullptr; int64_t cap_loss = 0;   // loss kernel's per-block partials: [blocks][2] {loss, kl} then [blocks][HP] column sums
   int64_t t = 0; int64_t steps_in_epoch = 0; int64_t last_launches = 0;
   std::vector<float> host_tmp;
   cudaStream_t copy_stream = nullptr;  // host->device staging of talos_ppo_update_host, overlapped with the steps
@@ -77,12 +78,14 @@ void ensure_weights_prepared(talos_ppo* p) {
 // One launch for the whole flat gradient: segment s of `dst` (n elements) = sum over `slabs` partial rows of length n,
 // added in a fixed order (eight slab lanes per column, each striding the slabs, then the eight lane sums in lane
 // order): deterministic and independent of the launch geometry.  Segments with slabs = 0 were written directly.
-struct GradSegs { float* dst[6]; const float* src[6]; int n[6]; int slabs[6]; int first_block[7]; };
+// The seventh segment is the loss kernel's per-block {loss, kl} sums; its block also writes the sample count behind them.
+constexpr int GRAD_SEGS = 7;
+struct GradSegs { float* dst[GRAD_SEGS]; const float* src[GRAD_SEGS]; int n[GRAD_SEGS]; int slabs[GRAD_SEGS]; int first_block[GRAD_SEGS + 1]; float count; };
 __global__ void __launch_bounds__(256)
 grad_gather_kernel(GradSegs g) {
   __shared__ float sh[8][33];
   int s = 0;
-  while (s < 5 && (int)blockIdx.x >= g.first_block[s + 1]) ++s;
+  while (s < GRAD_SEGS - 1 && (int)blockIdx.x >= g.first_block[s + 1]) ++s;
   const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
   const int c = ((int)blockIdx.x - g.first_block[s]) * 32 + cl;
   const int n = g.n[s], slabs = g.slabs[s];
@@ -100,6 +103,7 @@ grad_gather_kernel(GradSegs g) {
     for (int l = 0; l < 8; ++l) t += sh[l][cl];
     g.dst[s][c] = t;
   }
+  if (s == GRAD_SEGS - 1 && threadIdx.x == 0) { g.dst[s][2] = g.count; g.dst[s][3] = 0.f; }       // {loss, kl, count, 0}: the tail of the flat gradient
 }
 
 __global__ void unpack_heads_kernel(const float* __restrict__ z, int HP, int A, long long n, float* __restrict__ logits, float* __restrict__ values) {
@@ -177,12 +181,24 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   const int64_t H = c.hidden, HP = p->HP;
   const int64_t l0 = ctx->launches.load();
   float* tail = G + p->n_int;
-  TALOS_CHECK_CUDA(cudaMemsetAsync(tail, 0, 4 * sizeof(float), ctx->stream));      // Adam::zero_grad (src/ppo.rs:686); GEMMs overwrite the rest
   forward(p, obs, n);
-  // per-sample loss and its gradient w.r.t. [logits | value]; sums (denominator 1), divided by the global count in Adam
-  talos_status st = talos_ppo_loss_fwd_bwd(ctx, p->z, HP, p->z + c.n_actions, HP, actions, old_logp, adv, ret, n, c.n_actions, c.clip,
-                                           c.c_value, c.c_entropy, 1.0f, p->dz, HP, p->dz + c.n_actions, HP, tail);
-  if (st) throw talos_error(st, talos_last_error_string());
+  // per-sample loss and its gradient w.r.t. [logits | value]; sums (denominator 1), divided by the global count in Adam.
+  // For the action counts the loss kernel is specialised for, it also leaves the heads' bias gradient (column sums of
+  // its output) and the {loss, kl} sums as per-block partials for the gather kernel: no separate column-sum and
+  // statistics launches, and the tail of the flat gradient is written rather than cleared and added to.
+  talos_status st = TALOS_OK;
+  const int loss_blocks = (int)ceil_div(n, 128);
+  const bool loss_fused = p->loss_part && talos_ppo_loss_colsum_supported(c.n_actions, (int)HP) && (int64_t)loss_blocks * (2 + HP) <= p->cap_loss;
+  float* loss_cs = p->loss_part ? p->loss_part + 2 * (size_t)loss_blocks : nullptr;
+  if (loss_fused) {
+    talos_ppo_loss_launch(ctx, p->z, HP, p->z + c.n_actions, HP, actions, old_logp, adv, ret, n, c.n_actions, c.clip, c.c_value, c.c_entropy, 1.0f,
+                          p->dz, HP, p->dz + c.n_actions, HP, p->loss_part, loss_cs, (int)HP);
+  } else {
+    TALOS_CHECK_CUDA(cudaMemsetAsync(tail, 0, 4 * sizeof(float), ctx->stream));    // Adam::zero_grad (src/ppo.rs:686); GEMMs overwrite the rest
+    st = talos_ppo_loss_fwd_bwd(ctx, p->z, HP, p->z + c.n_actions, HP, actions, old_logp, adv, ret, n, c.n_actions, c.clip,
+                                c.c_value, c.c_entropy, 1.0f, p->dz, HP, p->dz + c.n_actions, HP, tail);
+    if (st) throw talos_error(st, talos_last_error_string());
+  }
   EpiArgs none{nullptr, nullptr, 0, nullptr, 0, 0, 0, 0};
   // Each gradient is either written straight into G or left as partial sums (split-K slabs of a weight-gradient
   // product, row-slab column sums of a bias gradient) that ONE gather kernel reduces into G at the end, instead of
@@ -227,7 +243,8 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   };
   // heads: dWh = h2^T.dz ; dbh = colsum(dz) ; dh2 = (dz.Wh^T) * (1 - h2^2)
   seg(0, G + p->o_wh, part_wh, H * HP, gemm_dw(p, H, HP, n, p->h2, H, p->dz, HP, G + p->o_wh, p->partials ? part_wh : nullptr, p->cap_wh));
-  bias_grad(1, p->dz, nullptr, HP, G + p->o_bh, part_bh);
+  if (loss_fused) { seg(1, G + p->o_bh, loss_cs, HP, loss_blocks); seg(6, tail, p->loss_part, 2, loss_blocks); gs.count = (float)n; }
+  else bias_grad(1, p->dz, nullptr, HP, G + p->o_bh, part_bh);
   backprop_hidden(2, p->dz, HP, p->o_wh, p->dh2, p->h2, G + p->o_b2, part_b2);
   // layer 2
   seg(3, G + p->o_w2, part_w2, H * H, gemm_dw(p, H, H, n, p->h1, H, p->dh2, H, G + p->o_w2, p->partials ? part_w2 : nullptr, p->cap_w2));
@@ -236,8 +253,8 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   seg(5, G + p->o_w1, part_w1, c.obs_dim * H, gemm_dw(p, c.obs_dim, H, n, obs, c.obs_dim, p->dh1, H, G + p->o_w1, p->partials ? part_w1 : nullptr, p->cap_w1));
   {
     int blocks = 0;
-    for (int i = 0; i < 6; ++i) { gs.first_block[i] = blocks; if (gs.slabs[i] > 0) blocks += (int)ceil_div(gs.n[i], 32); }
-    gs.first_block[6] = blocks;
+    for (int i = 0; i < GRAD_SEGS; ++i) { gs.first_block[i] = blocks; if (gs.slabs[i] > 0) blocks += (int)ceil_div(gs.n[i], 32); }
+    gs.first_block[GRAD_SEGS] = blocks;
     if (blocks > 0) { grad_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(gs); talos_launched(ctx, "grad_gather"); }
   }
   p->t += 1;
@@ -345,6 +362,7 @@ TALOS_API talos_status talos_ppo_create(talos_ctx* ctx, const talos_ppo_config* 
   alloc(&p->h1, mb * H); alloc(&p->h2, mb * H); alloc(&p->dh1, mb * H); alloc(&p->dh2, mb * H);
   alloc(&p->z, mb * p->HP); alloc(&p->dz, mb * p->HP);
   alloc(&p->step_stats, 4 * MAX_STEPS_PER_EPOCH);
+  p->cap_loss = up4(ceil_div(mb, 128) * (2 + p->HP)); alloc(&p->loss_part, p->cap_loss);
   if (cfg->mode != TALOS_MODE_FP32) {
     alloc(&p->w_hi, p->n_int);
     if (cfg->mode == TALOS_MODE_TF32X3) alloc(&p->w_lo, p->n_int);
@@ -363,7 +381,7 @@ TALOS_API talos_status talos_ppo_destroy(talos_ppo* p) {
   TALOS_ENTRY_BEGIN
   if (!p) return TALOS_OK;
   cudaSetDevice(p->ctx->device); cudaStreamSynchronize(p->ctx->stream);
-  for (float* q : {p->params, p->grads, p->m, p->v, p->h1, p->h2, p->dh1, p->dh2, p->z, p->dz, p->step_stats, p->w_hi, p->w_lo, p->partials}) cudaFree(q);
+  for (float* q : {p->params, p->grads, p->m, p->v, p->h1, p->h2, p->dh1, p->dh2, p->z, p->dz, p->step_stats, p->w_hi, p->w_lo, p->partials, p->loss_part}) cudaFree(q);
   for (cudaEvent_t ev : p->chunk_ready) cudaEventDestroy(ev);
   if (p->staging_free) cudaEventDestroy(p->staging_free);
   if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
