@@ -51,15 +51,22 @@ template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB, bool BPS,
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, const CUtensorMap& tmap_b_lo,
                                              const CUtensorMap* tmap_aux, const TcArgs& g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
-  constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
+  // DUAL (3xTF32, 32-column tiles): these products are bound by the NUMBER of MMA instructions (~90 cycles each however
+  // narrow), so hi.hi and hi.lo run as ONE 64-column MMA against [B hi | B lo] -- the lo tile sits right behind the hi
+  // tile in shared memory -- into a 64-column accumulator whose halves the epilogue warps add: two MMAs per k-step
+  // instead of three.
+  constexpr bool DUAL = X3 && BN == 32;
+  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
+  constexpr int B_STRIDE = DUAL ? 2 * B_BYTES : B_BYTES;             // bytes between the B tiles of consecutive stages
+  constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);
   constexpr int EPI_WARPS = TcRoles<X3, BPS, BN>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS, BN>::CONV_WARPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = sA + STAGES * A_BYTES;
-  uint8_t* sAlo = sB + STAGES * B_BYTES;
-  uint8_t* sBlo = sAlo + (X3 ? STAGES * A_BYTES : 0);
-  float* stage_all = (float*)(sBlo + (X3 ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
+  uint8_t* sAlo = sB + STAGES * B_STRIDE;
+  uint8_t* sBlo = DUAL ? sB + B_BYTES : sAlo + (X3 ? STAGES * A_BYTES : 0);
+  float* stage_all = (float*)(sAlo + (X3 ? STAGES * A_BYTES : 0) + ((X3 && !DUAL) ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
   uint64_t* bars = (uint64_t*)(stage_all + 8 * 32 * 32 * SBUF);
   uint64_t* aux_bars = bars; bars += AUXT ? 8 : 0;                   // AUXT: one barrier per epilogue warp for its activation tiles
   uint64_t* full = bars;                   // TMA -> (converter | issuer)
@@ -136,9 +143,9 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
           const bool load_b = !b_resident || issued < STAGES;
           ++issued;
           mbar_expect_tx(full + stage, A_BYTES + (load_b ? B_BYTES + (BPS ? B_BYTES : 0) : 0));
-          uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_BYTES;
+          uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_STRIDE;
           if (BPS && load_b) {
-            uint8_t* bl_dst = sBlo + stage * B_BYTES;
+            uint8_t* bl_dst = sBlo + stage * B_STRIDE;
             if (B_MN) { for (int j = 0; j < BN / 32; ++j) tma_load_3d(bl_dst + j * (BK * 128), &tmap_b_lo, nb * BN + 32 * j, kb * BK, bz, full + stage); }
             else tma_load_3d(bl_dst, &tmap_b_lo, kb * BK, nb * BN, bz, full + stage);
           }
@@ -174,16 +181,26 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
           const int buf = (c0 == kb0) ? run : (run ^ 1), c1 = min(kb1, c0 + ckb);
           if (!mbar_wait(tempty + buf, acc_phase[buf] ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * ACC_COLS);
           for (int kb = c0; kb < c1; ++kb) {
             // 3xTF32: the products that need no converted operand (hi.hi, and hi.lo when B arrives pre-split) are issued
             // as soon as the loads have landed, beside the converter; the rest once the lo tiles are written.
-            const bool early = X3 && g.early_pass;
+            const bool early = X3 && g.early_pass && !(DUAL && !BPS);    // (DUAL without a pre-split B has nothing to start early)
             if (!mbar_wait((X3 && !early ? conv : full) + stage, phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_BYTES);
-            const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_BYTES);
-            if (early) {
+            const uint32_t a_hi = smem_u32(sA + stage * A_BYTES), b_hi = smem_u32(sB + stage * B_STRIDE);
+            const uint32_t a_lo = smem_u32(sAlo + stage * A_BYTES), b_lo = smem_u32(sBlo + stage * B_STRIDE);
+            if (DUAL) {
+              const uint32_t idesc2 = (idesc & ~(0x3Fu << 17)) | ((uint32_t)(ACC_COLS >> 3) << 17);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)                                                                 // hi.[hi | lo]
+                tc_mma_tf32(d_tmem, make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay), idesc2,
+                            (kb > c0 || k > 0) ? 1u : 0u);
+              if (early) { if (!mbar_wait(conv + stage, phase, abort_flag)) { ok = false; break; } tc_fence_after(); }
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)                                                                 // lo.hi
+                tc_mma_tf32(d_tmem, make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lay), make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay), idesc, 1u);
+            } else if (early) {
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; ++k) {
                 const uint64_t da = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lay), db = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lay);
@@ -238,19 +255,20 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
       const int kb0 = ks * g.kb_per_split, kb1 = min(g.kb_total, kb0 + g.kb_per_split);
       const int run = tcount & 1, other = run ^ 1; ++tcount;
       const int ckb = g.chain_kb > 0 ? g.chain_kb : (kb1 - kb0);
-      const uint32_t t_run = tmem_base + (uint32_t)(run * BN), t_other = tmem_base + (uint32_t)(other * BN);
+      const uint32_t t_run = tmem_base + (uint32_t)(run * ACC_COLS), t_other = tmem_base + (uint32_t)(other * ACC_COLS);
       if (!mbar_wait(tfull + run, acc_phase[run], abort_flag)) { ok = false; break; }        // first chain: lands in the running buffer
       tc_fence_after();
       for (int c0 = kb0 + ckb; c0 < kb1 && ok; c0 += ckb) {                                   // further chains: fold, hand the buffer back
         if (!mbar_wait(tfull + other, acc_phase[other], abort_flag)) { ok = false; break; }
         tc_fence_after();
-        tc_fold_chain<BN, EPI_WARPS>(t_run, t_other, warp);
+        tc_fold_chain<ACC_COLS, EPI_WARPS>(t_run, t_other, warp);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty + other);
         acc_phase[other] ^= 1;
       }
       if (!ok) break;
+      if (DUAL) tc_fold_chain<BN, EPI_WARPS>(t_run, t_run + (uint32_t)BN, warp);       // (hi.hi + lo.hi) += hi.lo
       if (AUXT) {
         const int nit = it + (int)gridDim.x; int nmb = 0, nnb = 0;
         if (nit < items) tc_tile_coords(nit % tiles_mn, g.m_tiles, g.n_tiles, g.group_m, nmb, nnb);
@@ -289,7 +307,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
         if (!mbar_wait(full + stage, phase, abort_flag)) { ok = false; break; }
         // The split is elementwise, so it is oblivious to the swizzle: same offset in, same offset out.
         float4* ahi = (float4*)(sA + stage * A_BYTES); float4* alo = (float4*)(sAlo + stage * A_BYTES);
-        float4* bhi = (float4*)(sB + stage * B_BYTES); float4* blo = (float4*)(sBlo + stage * B_BYTES);
+        float4* bhi = (float4*)(sB + stage * B_STRIDE); float4* blo = (float4*)(sBlo + stage * B_STRIDE);
         constexpr int CONV_ITERS = (A_BYTES + (BPS ? 0 : B_BYTES)) / 16 / CONV_THREADS;
         static_assert((A_BYTES + (BPS ? 0 : B_BYTES)) % (16 * CONV_THREADS) == 0, "tile bytes must divide evenly over the converter threads");
 #pragma unroll 8
