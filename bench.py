@@ -565,6 +565,20 @@ def run_ours(args):
     value = args.steps * mb * world / (ms * 1e-3)
     repeats = {"timed_regions": len(regions), "steps_per_region": args.steps, "ms_per_step_median": ms / args.steps,
                "ms_per_step_min": srt[0] / args.steps, "ms_per_step_max": srt[-1] / args.steps, "value_is": "median region"}
+    # Per-launch device times of the step, warm (the way the step runs them, not the cold serialised times a profiler
+    # shows): five more steps with an event behind every launch; median per position.  Outside the timed regions.
+    step_launches = None
+    if rank == 0 and world == 1:
+        per_step = launches // max(1, args.steps)
+        ctx.timeline_begin()
+        for i in range(5):
+            one_step(tr, i)
+        marks = ctx.timeline_end()
+        if per_step > 0 and len(marks) == 5 * per_step:
+            step_launches = []
+            for j in range(per_step):
+                us = sorted(marks[k * per_step + j][1] for k in range(1, 5))      # (the first step's first mark includes the begin call)
+                step_launches.append([marks[per_step + j][0], round((us[1] + us[2]) / 2, 2)])
     if args.mode != "fp32" and not ctx.tensor_cores_active:
         raise SystemExit("bench.py: the tensor-core path is disabled on this context (its start-up self-check failed; run with "
                          "TALOS_DEBUG=1 to see which case): refusing to report the fp32 fallback as a %s figure" % args.mode)
@@ -644,6 +658,8 @@ def run_ours(args):
                "config": bench_config(world), "tensor_cores_active": ctx.tensor_cores_active,
                "tflops": value * FLOP_PER_SAMPLE / 1e12, "repeats": repeats, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
                "cpu_baseline": cpu, "other_modes": other_modes}
+        if step_launches is not None:
+            out["step_launches_warm_us"] = step_launches
         if dp is not None:
             out.update(dp)
         if gemm is not None:

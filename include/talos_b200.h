@@ -98,6 +98,13 @@ talos_status talos_free(talos_ctx* ctx, void* ptr);
 talos_status talos_ctx_trim(talos_ctx* ctx);
 /* stats4_host = {bytes handed out, bytes idle in the cache, cudaMalloc calls made, requests served from the cache}. */
 talos_status talos_ctx_memory_stats(talos_ctx* ctx, int64_t* stats4_host);
+/* Measurement aid, no counterpart in the reference: between _begin and _end every kernel launch made through this ctx is
+ * followed by an event on its stream (at most 512).  _end waits for the stream and writes, for the first `capacity`
+ * launches, the device time from the previous mark (the _begin call for the first) to the end of that launch in
+ * microseconds and the launch's name (NUL-terminated, `name_stride` bytes apart); *count_out = launches recorded.
+ * The events serialise nothing but cost about a microsecond each: not for timed regions. */
+talos_status talos_ctx_timeline_begin(talos_ctx* ctx);
+talos_status talos_ctx_timeline_end(talos_ctx* ctx, int32_t capacity, int32_t* count_out, float* us_out_host, char* names_out_host, int32_t name_stride);
 talos_status talos_memset_zero(talos_ctx* ctx, void* ptr, size_t bytes);
 talos_status talos_copy_from_host(talos_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 talos_status talos_copy_to_host(talos_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);

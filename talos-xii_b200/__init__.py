@@ -155,6 +155,18 @@ class Context:
     def tensor_cores_active(self):
         return bool(lib.talos_ctx_tensor_cores_active(self.handle))
 
+    def timeline_begin(self):
+        """Measurement aid: from here every launch through this context is followed by an event (see timeline_end)."""
+        lib.talos_ctx_timeline_begin(self.handle)
+
+    def timeline_end(self, capacity=512):
+        """Returns [(launch name, microseconds since the previous mark)] for the launches since timeline_begin."""
+        n = C.c_int32(); us = (C.c_float * capacity)(); stride = 32
+        names = C.create_string_buffer(capacity * stride)
+        lib.talos_ctx_timeline_end(self.handle, capacity, C.byref(n), us, names, stride)
+        k = min(n.value, capacity)
+        return [(names.raw[i * stride:(i + 1) * stride].split(b"\0", 1)[0].decode(), float(us[i])) for i in range(k)]
+
     @property
     def tensor_cores_state(self):
         """1: in use; 0: not probed yet; -1: the start-up self-check failed and the fp32 kernel serves every mode."""

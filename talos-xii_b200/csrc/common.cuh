@@ -56,7 +56,10 @@ struct talos_ctx {
   unsigned dbg_wait_spins = 0;     // test hook (talos_debug_gemm_stall): poll limit of the GEMM kernels' bounded waits, 0 = default
   int dbg_skip_kb = -1;            // test hook: k-block the first CTA's loader leaves out, -1 = none
   struct talos_pool* pool = nullptr;   // caching device allocator behind talos_malloc / talos_free (ctx.cu)
+  struct talos_timeline* timeline = nullptr;   // measurement aid (talos_ctx_timeline_begin): one event per launch while recording
 };
+// Records an event behind the launch just made (ctx.cu); only called while a timeline is being recorded.
+void talos_timeline_mark(talos_ctx* ctx, const char* what);
 
 // Device-side error codes written to talos_ctx::dev_status (first writer wins is not required: any non-zero value reports).
 #define TALOS_DEV_TIMEOUT_BASE 1000    // + CTA index % 1000 (+ 1000 from the CTA-pair kernel): a bounded mbarrier / flag wait gave up  -> TALOS_ERR_TIMEOUT
@@ -86,6 +89,7 @@ inline void talos_launched(talos_ctx* ctx, const char* what) {
   ctx->launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw talos_error(TALOS_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  if (ctx->timeline) talos_timeline_mark(ctx, what);
 }
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -1,5 +1,6 @@
 // Context lifetime, scratch buffer, error string, seeded synthetic-input generators.
 #include <math.h>
+#include <stdio.h>
 #include <string.h>
 
 #include <mutex>
@@ -94,11 +95,13 @@ TALOS_API talos_status talos_ctx_create(int32_t device, void* stream, talos_ctx*
   TALOS_ENTRY_END
 }
 
+static void timeline_destroy(talos_timeline* t);
 TALOS_API talos_status talos_ctx_destroy(talos_ctx* ctx) {
   TALOS_ENTRY_BEGIN
   if (!ctx) return TALOS_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  timeline_destroy(ctx->timeline);
   if (ctx->pool) {
     pool_trim(ctx);
     for (auto& kv : ctx->pool->live) cudaFree(kv.first);          // blocks the host never returned
@@ -213,6 +216,55 @@ TALOS_API talos_status talos_ctx_memory_stats(talos_ctx* ctx, int64_t* stats4) {
   stats4[2] = ctx->pool->driver_allocs; stats4[3] = ctx->pool->reuses;
   TALOS_ENTRY_END
 }
+// ---- launch timeline (measurement aid): while recording, every launch is followed by an event on the ctx stream ----
+struct talos_timeline {
+  static constexpr int MAX_MARKS = 512;
+  cudaEvent_t start = nullptr;
+  std::vector<cudaEvent_t> events;       // created once, reused
+  std::vector<const char*> names;        // string literals passed to talos_launched
+  int used = 0;
+};
+void talos_timeline_mark(talos_ctx* ctx, const char* what) {
+  talos_timeline* t = ctx->timeline;
+  if (!t || t->used >= talos_timeline::MAX_MARKS) return;
+  if ((int)t->events.size() <= t->used) { cudaEvent_t e; if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; } t->events.push_back(e); t->names.push_back(what); }
+  t->names[t->used] = what;
+  cudaEventRecord(t->events[t->used], ctx->stream);
+  t->used += 1;
+}
+static void timeline_destroy(talos_timeline* t) {
+  if (!t) return;
+  for (cudaEvent_t e : t->events) cudaEventDestroy(e);
+  if (t->start) cudaEventDestroy(t->start);
+  delete t;
+}
+TALOS_API talos_status talos_ctx_timeline_begin(talos_ctx* ctx) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  if (!ctx->timeline) { ctx->timeline = new talos_timeline(); TALOS_CHECK_CUDA(cudaEventCreate(&ctx->timeline->start)); }
+  ctx->timeline->used = 0;
+  TALOS_CHECK_CUDA(cudaEventRecord(ctx->timeline->start, ctx->stream));
+  TALOS_ENTRY_END
+}
+TALOS_API talos_status talos_ctx_timeline_end(talos_ctx* ctx, int32_t capacity, int32_t* count_out, float* us_out, char* names_out, int32_t name_stride) {
+  TALOS_ENTRY_BEGIN
+  talos_check_ctx(ctx);
+  TALOS_REQUIRE(count_out != nullptr && capacity >= 0 && (capacity == 0 || (us_out && names_out && name_stride > 1)), TALOS_ERR_ARG, "bad timeline buffers");
+  talos_timeline* t = ctx->timeline;
+  TALOS_REQUIRE(t != nullptr, TALOS_ERR_ARG, "no timeline is being recorded");
+  talos_sync_and_check(ctx);
+  const int n = std::min<int>(t->used, capacity);
+  for (int i = 0; i < n; ++i) {
+    float ms = 0.f;
+    TALOS_CHECK_CUDA(cudaEventElapsedTime(&ms, i ? t->events[i - 1] : t->start, t->events[i]));
+    us_out[i] = ms * 1000.f;
+    snprintf(names_out + (size_t)i * name_stride, (size_t)name_stride, "%s", t->names[i]);
+  }
+  *count_out = t->used;
+  timeline_destroy(t); ctx->timeline = nullptr;
+  TALOS_ENTRY_END
+}
+
 TALOS_API talos_status talos_memset_zero(talos_ctx* ctx, void* ptr, size_t bytes) {
   TALOS_ENTRY_BEGIN
   talos_check_ctx(ctx);

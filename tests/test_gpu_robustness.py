@@ -184,3 +184,21 @@ def test_caching_allocator_reuses_blocks_and_refuses_foreign_pointers(talos, ctx
     _expect(talos, talos.ERR_ARG, lambda: talos.lib.talos_free(ctx.handle, ctypes.c_void_p(0x1000)))
     talos.lib.talos_ctx_trim(ctx.handle)
     assert st()[1] == 0
+
+
+def test_launch_timeline_reports_every_launch_in_order(talos, ctx):
+    # measurement aid: one event behind every launch between begin and end; times are positive, names in launch order
+    import torch
+    a = torch.randn(4096, 256, device="cuda:0"); out = torch.empty(256, device="cuda:0")
+    l0 = ctx.launches
+    ctx.timeline_begin()
+    for _ in range(3):
+        talos.lib.talos_colsum(ctx.handle, talos.ptr(a), talos.ptr(out), 4096, 256, 0)
+    marks = ctx.timeline_end()
+    assert len(marks) == ctx.launches - l0 and len(marks) >= 3
+    assert all(us > 0 for _, us in marks) and all(name.startswith("colsum") for name, _ in marks)
+    l1 = ctx.launches
+    talos.lib.talos_colsum(ctx.handle, talos.ptr(a), talos.ptr(out), 4096, 256, 0)        # recording is off again
+    ctx.synchronize()
+    assert ctx.launches > l1
+    assert torch.allclose(out, a.sum(0), rtol=1e-4, atol=1e-3)
