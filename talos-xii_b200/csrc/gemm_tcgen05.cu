@@ -344,12 +344,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ TcArgs g) {
   gemm_tc_body<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF, false>(tmap_a, tmap_b, tmap_c, tmap_b_lo, nullptr, g);
 }
-// The fused input-gradient configurations (3xTF32, prepared weights, both operands K-major): one more tensor map.
-template <int BN, int SBUF>
-__global__ void __launch_bounds__((TcRoles<true, true>::THREADS), 1)
+// The fused input-gradient configurations (prepared weights, both operands K-major): one more tensor map.  3xTF32 with the
+// pre-split weights (two stages), or TF32 with the rounded weights (three stages).
+template <int BN, int STAGES, bool X3, int SBUF>
+__global__ void __launch_bounds__((TcRoles<X3, X3>::THREADS), 1)
 gemm_tc_aux_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                    const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ CUtensorMap tmap_aux, const __grid_constant__ TcArgs g) {
-  gemm_tc_body<BN, 2, true, false, false, 1, true, SBUF, true>(tmap_a, tmap_b, tmap_c, tmap_b_lo, &tmap_aux, g);
+  gemm_tc_body<BN, STAGES, X3, false, false, 1, X3, SBUF, true>(tmap_a, tmap_b, tmap_c, tmap_b_lo, &tmap_aux, g);
 }
 
 // Dense copy of a [rows][cols] matrix (pitch ld) rounded to TF32 with round-to-nearest.  In the fast TF32
@@ -623,7 +624,8 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   int grid = (int)std::min<int64_t>((int64_t)tiles * splits * g.batch, ctx->sm_count);
   // The input gradient of a tanh layer takes tanh' and the bias gradient's column sums into its epilogue: the K <= 64
   // configuration (128-column tiles, two staging buffers) and the 256-column one (a single staging buffer).
-  const bool aux_cfg = presplit && !a_mn && !b_mn && !pair && splits == 1 && (short_k || bn == 256) && g.n_tiles * (bn / 64) <= 4;
+  const bool aux_x3 = presplit && (short_k || bn == 256), aux_tf32 = !x3 && b_given && bn == 256;
+  const bool aux_cfg = (aux_x3 || aux_tf32) && !batched && !a_mn && !b_mn && !pair && splits == 1 && g.n_tiles * (bn / 64) <= 4;
   const bool auxt = extra && extra->tanh_saved && extra->colsum_part && extra->colsum_slabs_out && aux_cfg && !(N & 31) && plain_epi && g.tma_out &&
                     !(((uintptr_t)extra->tanh_saved) & 15) && !(extra->ld_saved & 3) && extra->colsum_floats >= (size_t)4 * grid * N &&
                     !getenv("TALOS_TC_NO_FUSED_DACT");
@@ -632,15 +634,14 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   if (auxt) {
     g.colsum_part = extra->colsum_part;
-    if (bn == 128) {
-      const size_t smem = tc_smem_bytes<128, 2, true, 2>() + 64;
-      TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      gemm_tc_aux_kernel<128, 2><<<grid, TcRoles<true, true>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g);
-    } else {
-      const size_t smem = tc_smem_bytes<256, 2, true, 1>() + 64;
-      TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      gemm_tc_aux_kernel<256, 1><<<grid, TcRoles<true, true>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g);
-    }
+#define TALOS_TC_AUX(BNv, ST, X3v, SB)                                                                                              \
+  { const size_t smem = tc_smem_bytes<BNv, ST, X3v, SB>() + 64;                                                                     \
+    TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<BNv, ST, X3v, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    gemm_tc_aux_kernel<BNv, ST, X3v, SB><<<grid, TcRoles<X3v, X3v>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g); }
+    if (!x3) TALOS_TC_AUX(256, 3, false, 2)
+    else if (bn == 128) TALOS_TC_AUX(128, 2, true, 2)
+    else TALOS_TC_AUX(256, 2, true, 1)
+#undef TALOS_TC_AUX
     talos_launched(ctx, "gemm_tcgen05");
     *extra->colsum_slabs_out = 4 * grid;
     return;

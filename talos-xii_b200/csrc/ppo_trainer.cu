@@ -222,9 +222,9 @@ void step(talos_ppo* p, talos_comm* comm, const float* obs, const int32_t* actio
   // gradient's column sums at the same time.
   auto backprop_hidden = [&](int i, const float* dz_next, int64_t k, int64_t w_off, float* dh, const float* h_saved, float* db, float* part) {
     if (H % 4 == 0 && H <= 1024) {                                              // what the streaming kernel takes (buffers are aligned)
-      // Short reductions (the heads' K = 32) take the factor and the column sums into the GEMM's own epilogue, which
-      // fetches the saved activation tiles by TMA: no streaming pass at all.
-      if (p->partials && p->w_hi && p->cfg.mode == TALOS_MODE_TF32X3) {
+      // The tensor-core modes take the factor and the column sums into the GEMM's own epilogue, which fetches the saved
+      // activation tiles by TMA: no streaming pass at all (the launcher says whether the shape qualified).
+      if (p->partials && p->w_hi && (p->cfg.mode == TALOS_MODE_TF32X3 || p->cfg.mode == TALOS_MODE_TF32)) {
         int slabs = 0;
         TcExtra x; x.b_hi = p->w_hi + w_off; x.b_lo = p->w_lo ? p->w_lo + w_off : nullptr;
         x.tanh_saved = h_saved; x.ld_saved = H; x.colsum_part = part; x.colsum_floats = (size_t)p->cap_b; x.colsum_slabs_out = &slabs;

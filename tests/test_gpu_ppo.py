@@ -142,10 +142,12 @@ def test_ppo_minibatch_split_invariance(talos, ctx):
 
 
 @pytest.mark.needs_tensor_cores
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("N", [1000, 4096 + 37])
-def test_fused_tanh_backward_epilogue_on_ragged_minibatches(talos, ctx, N, monkeypatch):
-    # 3xTF32, hidden 256, heads padded to K = 32: both input-gradient GEMMs (K = 32 through 128-column tiles, K = 256
-    # through 256-column tiles) take tanh'(h) and the column sums of the layer's bias gradient into their own epilogue.
+def test_fused_tanh_backward_epilogue_on_ragged_minibatches(talos, ctx, N, mode, monkeypatch):
+    # hidden 256, heads padded to K = 32: both input-gradient GEMMs (3xTF32: K = 32 through 128-column tiles, K = 256
+    # through 256-column tiles; TF32: 256-column tiles, three stages) take tanh'(h) and the column sums of the layer's
+    # bias gradient into their own epilogue.
     # Row counts that end inside a 32-row chunk and inside a 128-row tile; every gradient against the oracle, and
     # against the route with the separate streaming passes.
     obs, actions, adv, ret, params = make_problem(N, 64, 256, 16, seed=90)
@@ -155,11 +157,11 @@ def test_fused_tanh_backward_epilogue_on_ragged_minibatches(talos, ctx, N, monke
     for route in ("fused", "separate"):
         if route == "separate":
             monkeypatch.setenv("TALOS_TC_NO_FUSED_DACT", "1")
-        tr = talos.PPOTrainer(ctx, talos.PpoConfig(64, 256, 16, N, 1)); tr.set_params(params)
+        tr = talos.PPOTrainer(ctx, talos.PpoConfig(64, 256, 16, N, mode)); tr.set_params(params)
         tr.step(dev(obs), dev(actions), dev(old), dev(adv), dev(ret), N)
         got[route] = (tr.get_grads(), tr.launches_per_step)
         tr.close()
     for k in g_ref:
-        assert rel_err(got["fused"][0][k], g_ref[k]) <= 2 * TOL[1], (k, rel_err(got["fused"][0][k], g_ref[k]))
+        assert rel_err(got["fused"][0][k], g_ref[k]) <= 2 * TOL[mode], (k, rel_err(got["fused"][0][k], g_ref[k]))
         assert rel_err(got["fused"][0][k], got["separate"][0][k]) <= 2e-6, k
     assert got["fused"][1] == got["separate"][1] - 2          # two streaming passes less
