@@ -16,8 +16,8 @@
 
 namespace {
 
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
   unsigned long long v;
@@ -38,11 +38,11 @@ xchg_adam_kernel(XchgAdamArgs a) {
   __shared__ int sh_ok;
   __shared__ float sh_count;
   if (threadIdx.x == 0) {
-    // Publish: the local sums were written by earlier kernels on this stream, so they are complete; the fence orders
-    // them before the flag for observers on other GPUs.
+    // Publish: the local sums were written by earlier kernels on this stream, so they are complete; ONE system fence
+    // orders them before the flags for observers on other GPUs, and the flag stores themselves go out back to back.
     if (blockIdx.x == 0 && !a.skip_signal) {
       __threadfence_system();
-      for (int r = 0; r < a.world; ++r) st_release_sys(a.peer_flags[r] + a.rank, a.seq);
+      for (int r = 0; r < a.world; ++r) st_relaxed_sys(a.peer_flags[r] + a.rank, a.seq);
     }
     // Wait for every rank's publication of this sequence number in OUR area (bounded).
     int ok = 1;
@@ -56,21 +56,33 @@ xchg_adam_kernel(XchgAdamArgs a) {
       }
     }
     if (!ok) atomicExch(a.status, TALOS_DEV_TIMEOUT_BASE + 1900 + a.rank);
-    float cnt = 0.f;
-    if (ok) for (int r = 0; r < a.world; ++r) cnt += ld_peer4(a.slot[r] + a.n).z;       // tail = {sum loss, sum kl, count, -}
-    sh_ok = ok; sh_count = cnt;
+    sh_ok = ok;
   }
   __syncthreads();
   if (!sh_ok) return;                                   // nothing is updated on a rank that gave up
-  const float coef = 1.f / fmaxf(sh_count, 1.f);
   const long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long n4 = a.n >> 2;
-  if (i4 > n4) return;
-  float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int r = 0; r < a.world; ++r) {                  // rank order: the same sum on every rank
-    const float4 x = ld_peer4(a.slot[r] + 4 * i4);
-    g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+  const bool active = i4 <= n4;
+  // Every peer load of this thread is issued before the first one is used: a remote load is a round trip over NVLink,
+  // and with eight ranks eight dependent round trips were most of the exchange's cost.
+  float4 x[TALOS_MAX_RANKS], t[TALOS_MAX_RANKS];
+#pragma unroll
+  for (int r = 0; r < TALOS_MAX_RANKS; ++r) if (r < a.world && active) x[r] = ld_peer4(a.slot[r] + 4 * i4);
+  if (threadIdx.x == 0) {                                // tail = {sum loss, sum kl, count, -}
+#pragma unroll
+    for (int r = 0; r < TALOS_MAX_RANKS; ++r) if (r < a.world) t[r] = ld_peer4(a.slot[r] + a.n);
+    float cnt = 0.f;
+#pragma unroll
+    for (int r = 0; r < TALOS_MAX_RANKS; ++r) if (r < a.world) cnt += t[r].z;
+    sh_count = cnt;
   }
+  __syncthreads();
+  if (!active) return;
+  const float coef = 1.f / fmaxf(sh_count, 1.f);
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < TALOS_MAX_RANKS; ++r)              // rank order: the same sum on every rank
+    if (r < a.world) { g.x += x[r].x; g.y += x[r].y; g.z += x[r].z; g.w += x[r].w; }
   if (a.grads_out) ((float4*)a.grads_out)[i4] = g;     // the reduced sums (and, in the last group, the reduced tail)
   if (i4 == n4) { if (a.stats_out) ((float4*)a.stats_out)[0] = g; return; }
   float4 p = ((float4*)a.params)[i4], m = ((float4*)a.m)[i4], v = ((float4*)a.v)[i4];
