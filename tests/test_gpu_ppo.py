@@ -143,21 +143,22 @@ def test_ppo_minibatch_split_invariance(talos, ctx):
 
 @pytest.mark.needs_tensor_cores
 @pytest.mark.parametrize("mode", [1, 2])
-@pytest.mark.parametrize("N", [1000, 4096 + 37])
-def test_fused_tanh_backward_epilogue_on_ragged_minibatches(talos, ctx, N, mode, monkeypatch):
+@pytest.mark.parametrize("N,hidden", [(1000, 256), (4096 + 37, 256), (2048 + 5, 192)])
+def test_fused_tanh_backward_epilogue_on_ragged_minibatches(talos, ctx, N, hidden, mode, monkeypatch):
     # hidden 256, heads padded to K = 32: both input-gradient GEMMs (3xTF32: K = 32 through 128-column tiles, K = 256
     # through 256-column tiles; TF32: 256-column tiles, three stages) take tanh'(h) and the column sums of the layer's
     # bias gradient into their own epilogue.
-    # Row counts that end inside a 32-row chunk and inside a 128-row tile; every gradient against the oracle, and
-    # against the route with the separate streaming passes.
-    obs, actions, adv, ret, params = make_problem(N, 64, 256, 16, seed=90)
+    # Row counts that end inside a 32-row chunk and inside a 128-row tile, and a width (192) whose last column panel is
+    # half outside the matrix; every gradient against the oracle, and against the route with the separate streaming
+    # passes.
+    obs, actions, adv, ret, params = make_problem(N, 64, hidden, 16, seed=90)
     model = om.MlpActorCritic(params); old = orc.f32r(model.log_prob(obs, actions))
     g_ref, _, _ = model.grads(obs, actions, old, adv, ret)
     got = {}
     for route in ("fused", "separate"):
         if route == "separate":
             monkeypatch.setenv("TALOS_TC_NO_FUSED_DACT", "1")
-        tr = talos.PPOTrainer(ctx, talos.PpoConfig(64, 256, 16, N, mode)); tr.set_params(params)
+        tr = talos.PPOTrainer(ctx, talos.PpoConfig(64, hidden, 16, N, mode)); tr.set_params(params)
         tr.step(dev(obs), dev(actions), dev(old), dev(adv), dev(ret), N)
         got[route] = (tr.get_grads(), tr.launches_per_step)
         tr.close()
