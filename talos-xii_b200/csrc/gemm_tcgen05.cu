@@ -36,10 +36,12 @@ namespace {
 // Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, then the epilogue warps, then (3xTF32) the converter
 // warps.  When both operands are split in the kernel (no pre-split B: the weight-gradient products, whose epilogue
 // runs once per 16 k-blocks) the converter is the busy role, so it gets eight warps and the epilogue four.
-template <bool X3, bool BPS, int BN = 256> struct TcRoles {
+// EW: epilogue warps when not 0 (16 for the K <= 64 configurations, which are all epilogue: four warps per TMEM lane
+// quadrant, one 32-column chunk of a 128-column tile each).
+template <bool X3, bool BPS, int BN = 256, int EW = 0> struct TcRoles {
   // (narrow tiles with a pre-split B are converter-bound too: their epilogue moves 32 or 64 columns a tile)
   static constexpr bool CONV_HEAVY = X3 && (!BPS || BN <= 64);
-  static constexpr int EPI_WARPS = CONV_HEAVY ? 4 : 8;
+  static constexpr int EPI_WARPS = EW ? EW : (CONV_HEAVY ? 4 : 8);
   static constexpr int CONV_WARPS = X3 ? (CONV_HEAVY ? 8 : 4) : 0;
   static constexpr int THREADS = (2 + EPI_WARPS + CONV_WARPS) * 32;       // 448 (3xTF32) or 320 (TF32)
 };
@@ -47,7 +49,7 @@ template <bool X3, bool BPS, int BN = 256> struct TcRoles {
 // SBUF: staging buffers per epilogue warp (2 where the configuration leaves the shared memory for it).
 // AUXT: the epilogue multiplies by tanh'(saved activation), fetching the activation tiles by TMA (tmap_aux), and
 // accumulates the column sums of what it stores (see tc_epilogue_tile_aux).
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB, bool BPS, int SBUF, bool AUXT>
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB, bool BPS, int SBUF, bool AUXT, int EW = 0>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, const CUtensorMap& tmap_b_lo,
                                              const CUtensorMap* tmap_aux, const TcArgs& g) {
   constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
@@ -59,7 +61,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
   constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
   constexpr int B_STRIDE = DUAL ? 2 * B_BYTES : B_BYTES;             // bytes between the B tiles of consecutive stages
   constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);
-  constexpr int EPI_WARPS = TcRoles<X3, BPS, BN>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS, BN>::CONV_WARPS;
+  constexpr int EPI_WARPS = TcRoles<X3, BPS, BN, EW>::EPI_WARPS, CONV_WARPS = TcRoles<X3, BPS, BN, EW>::CONV_WARPS;
+  constexpr int STAGE_WARPS = EPI_WARPS > 8 ? EPI_WARPS : 8;        // staging buffers (and AUXT barriers) are laid out for at least eight warps
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
@@ -67,8 +70,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
   uint8_t* sAlo = sB + STAGES * B_STRIDE;
   uint8_t* sBlo = DUAL ? sB + B_BYTES : sAlo + (X3 ? STAGES * A_BYTES : 0);
   float* stage_all = (float*)(sAlo + (X3 ? STAGES * A_BYTES : 0) + ((X3 && !DUAL) ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
-  uint64_t* bars = (uint64_t*)(stage_all + 8 * 32 * 32 * SBUF);
-  uint64_t* aux_bars = bars; bars += AUXT ? 8 : 0;                   // AUXT: one barrier per epilogue warp for its activation tiles
+  uint64_t* bars = (uint64_t*)(stage_all + STAGE_WARPS * 32 * 32 * SBUF);
+  uint64_t* aux_bars = bars; bars += AUXT ? STAGE_WARPS : 0;                   // AUXT: one barrier per epilogue warp for its activation tiles
   uint64_t* full = bars;                   // TMA -> (converter | issuer)
   uint64_t* conv = full + STAGES;          // converter -> issuer (X3)
   uint64_t* empty = conv + STAGES;         // issuer (commit) -> TMA
@@ -81,7 +84,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(conv + s, CONV_WARPS ? CONV_WARPS : 1); mbar_init(empty + s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull + a, 1); mbar_init(tempty + a, EPI_WARPS); }
-    if (AUXT) for (int w = 0; w < 8; ++w) mbar_init(aux_bars + w, 1);
+    if (AUXT) for (int w = 0; w < STAGE_WARPS; ++w) mbar_init(aux_bars + w, 1);
     abort_flag[0] = 0; abort_flag[1] = (int)g.wait_spins;
     fence_barrier_init();
   }
@@ -247,7 +250,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
     float* const my_stage = stage_all + (warp - 2) * (32 * 32 * SBUF); uint64_t* const aux_bar = aux_bars + (warp - 2);
     if (AUXT && (int)blockIdx.x < items && lane == 0) {        // the first chunk's saved-activation tile, into the first staging buffer
       int mb0, nb0; tc_tile_coords((int)blockIdx.x % tiles_mn, g.m_tiles, g.n_tiles, g.group_m, mb0, nb0);
-      tc_aux_request(tmap_aux, my_stage, aux_bar, nb0 * BN + ((warp - 2) >> 2) * (BN / 2), (long long)mb0 * BM + (warp & 3) * 32);
+      tc_aux_request(tmap_aux, my_stage, aux_bar, nb0 * BN + ((warp - 2) >> 2) * (BN / (EPI_WARPS / 4)), (long long)mb0 * BM + (warp & 3) * 32);
     }
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int bz = it / per_batch, r = it - bz * per_batch;
@@ -269,10 +272,10 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
       }
       if (!ok) break;
       if (DUAL) tc_fold_chain<BN, EPI_WARPS>(t_run, t_run + (uint32_t)BN, warp);       // (hi.hi + lo.hi) += hi.lo
-      if (AUXT) {
+      if constexpr (AUXT) {
         const int nit = it + (int)gridDim.x; int nmb = 0, nnb = 0;
         if (nit < items) tc_tile_coords(nit % tiles_mn, g.m_tiles, g.n_tiles, g.group_m, nmb, nnb);
-        if (!tc_epilogue_tile_aux<BN, SBUF>(g, &tmap_c, tmap_aux, t_run, warp, lane, my_stage, aux_bar, abort_flag,
+        if (!tc_epilogue_tile_aux<BN, SBUF, EPI_WARPS>(g, &tmap_c, tmap_aux, t_run, warp, lane, my_stage, aux_bar, abort_flag,
                                             (long long)mb * BM, nb, nit < items, (long long)nmb * BM, nnb, store_count, aux_st)) { ok = false; break; }
       } else {
         tc_epilogue_tile<BN, EPI_WARPS, SBUF>(g, &tmap_c, t_run, warp, lane, my_stage, (long long)mb * BM, nb, ks, bz, store_count);
@@ -288,10 +291,10 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
       // this warp's column sums over all the tiles of the CTA: one partial row per (CTA, lane quadrant); a warp owns
       // half of the columns of each panel, zero where it had no tile
       float* row = g.colsum_part + ((size_t)blockIdx.x * 4 + (warp & 3)) * g.N;
-      const int half = (warp - 2) >> 2; constexpr int CHUNKS = BN / 64;
+      const int half = (warp - 2) >> 2; constexpr int PART_COLS = BN / (EPI_WARPS / 4), CHUNKS = PART_COLS / 32;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {                            // j = (column panel) * CHUNKS + (32-column chunk of this warp's half)
-        const int col = (j / CHUNKS) * BN + half * (BN / 2) + (j % CHUNKS) * 32 + lane;
+      for (int j = 0; j < 4; ++j) {                            // j = (column panel) * CHUNKS + (32-column chunk of this warp's share)
+        const int col = (j / CHUNKS) * BN + half * PART_COLS + (j % CHUNKS) * 32 + lane;
         if ((j / CHUNKS) < g.n_tiles && col < g.N) row[col] = aux_st.acc[j];
       }
     }
@@ -338,19 +341,19 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
-__global__ void __launch_bounds__((TcRoles<X3, BPS, BN>::THREADS), MINB)
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1, int EW = 0>
+__global__ void __launch_bounds__((TcRoles<X3, BPS, BN, EW>::THREADS), MINB)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ TcArgs g) {
-  gemm_tc_body<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF, false>(tmap_a, tmap_b, tmap_c, tmap_b_lo, nullptr, g);
+  gemm_tc_body<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF, false, EW>(tmap_a, tmap_b, tmap_c, tmap_b_lo, nullptr, g);
 }
 // The fused input-gradient configurations (prepared weights, both operands K-major): one more tensor map.  3xTF32 with the
 // pre-split weights (two stages), or TF32 with the rounded weights (three stages).
-template <int BN, int STAGES, bool X3, int SBUF>
-__global__ void __launch_bounds__((TcRoles<X3, X3>::THREADS), 1)
+template <int BN, int STAGES, bool X3, int SBUF, int EW = 0>
+__global__ void __launch_bounds__((TcRoles<X3, X3, BN, EW>::THREADS), 1)
 gemm_tc_aux_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                    const __grid_constant__ CUtensorMap tmap_b_lo, const __grid_constant__ CUtensorMap tmap_aux, const __grid_constant__ TcArgs g) {
-  gemm_tc_body<BN, STAGES, X3, false, false, 1, X3, SBUF, true>(tmap_a, tmap_b, tmap_c, tmap_b_lo, &tmap_aux, g);
+  gemm_tc_body<BN, STAGES, X3, false, false, 1, X3, SBUF, true, EW>(tmap_a, tmap_b, tmap_c, tmap_b_lo, &tmap_aux, g);
 }
 
 // Dense copy of a [rows][cols] matrix (pitch ld) rounded to TF32 with round-to-nearest.  In the fast TF32
@@ -455,27 +458,27 @@ bool make_out_tmap(CUtensorMap* out, const float* base, int64_t slabs, int64_t r
   return tmap_cached(TmapKey{base, slabs, rows, cols, ld, slab_stride, -1}, out, encode_output_map);
 }
 
-template <int BN, int STAGES, bool X3, int SBUF = 1>
+template <int BN, int STAGES, bool X3, int SBUF = 1, int EW = 0>
 size_t tc_smem_bytes() {
-  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + 8 * 32 * 32 * 4 * SBUF + (3 * STAGES + 4) * 8 + 16 + 1024;
+  return (size_t)STAGES * (BM * BK * 4 + BN * BK * 4) * (X3 ? 2 : 1) + (EW > 8 ? EW : 8) * 32 * 32 * 4 * SBUF + (3 * STAGES + 4) * 8 + 16 + 1024;
 }
 
-template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1>
+template <int BN, int STAGES, bool X3, bool A_MN, bool B_MN, int MINB = 1, bool BPS = false, int SBUF = 1, int EW = 0>
 void launch_one(talos_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tbl, const TcArgs& g, int grid) {
-  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF>;
-  size_t smem = tc_smem_bytes<BN, STAGES, X3, SBUF>();
+  auto kern = gemm_tc_kernel<BN, STAGES, X3, A_MN, B_MN, MINB, BPS, SBUF, EW>;
+  size_t smem = tc_smem_bytes<BN, STAGES, X3, SBUF, EW>();
   TALOS_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, TcRoles<X3, BPS, BN>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
+  kern<<<grid, TcRoles<X3, BPS, BN, EW>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, g);
   talos_launched(ctx, "gemm_tcgen05");
 }
 
-template <int BN, int STAGES, bool X3, int MINB = 1, bool BPS = false, int SBUF = 1>
+template <int BN, int STAGES, bool X3, int MINB = 1, bool BPS = false, int SBUF = 1, int EW = 0>
 void launch_major(talos_ctx* ctx, bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tbl,
                   const TcArgs& g, int grid) {
-  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
-  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
-  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
-  else launch_one<BN, STAGES, X3, true, true, MINB, BPS, SBUF>(ctx, ta, tb, tc, tbl, g, grid);
+  if (!a_mn && !b_mn) launch_one<BN, STAGES, X3, false, false, MINB, BPS, SBUF, EW>(ctx, ta, tb, tc, tbl, g, grid);
+  else if (!a_mn && b_mn) launch_one<BN, STAGES, X3, false, true, MINB, BPS, SBUF, EW>(ctx, ta, tb, tc, tbl, g, grid);
+  else if (a_mn && !b_mn) launch_one<BN, STAGES, X3, true, false, MINB, BPS, SBUF, EW>(ctx, ta, tb, tc, tbl, g, grid);
+  else launch_one<BN, STAGES, X3, true, true, MINB, BPS, SBUF, EW>(ctx, ta, tb, tc, tbl, g, grid);
 }
 
 static inline bool x3_mode(int mode) { return mode == TALOS_MODE_TF32X3; }
@@ -497,6 +500,8 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   // chunk overlaps the arithmetic of the next.
   const bool short_k = !batched && x3 && bn == 256 && K <= 64 && (b_given || (opB == TALOS_OP_N ? K * N : N * K) <= (1 << 20)) && !getenv("TALOS_TC_NO_SHORTK");
   if (short_k) bn = 128;
+  // (that configuration is all epilogue: sixteen epilogue warps, one 32-column chunk of a tile each, instead of eight with two)
+  const bool wide_epi = short_k && !getenv("TALOS_TC_NO_WIDE_EPI");
   TcArgs g;
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.C = C; g.ldc = ldc; g.epi = epi; g.status = ctx->dev_status; g.partial = nullptr;
   g.batch = (int)std::max<int64_t>(bt.batch, 1); g.stride_c = batched ? bt.stride_c : 0;
@@ -634,13 +639,14 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
   TALOS_REQUIRE(ok, TALOS_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   if (auxt) {
     g.colsum_part = extra->colsum_part;
-#define TALOS_TC_AUX(BNv, ST, X3v, SB)                                                                                              \
-  { const size_t smem = tc_smem_bytes<BNv, ST, X3v, SB>() + 64;                                                                     \
-    TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<BNv, ST, X3v, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    gemm_tc_aux_kernel<BNv, ST, X3v, SB><<<grid, TcRoles<X3v, X3v>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g); }
-    if (!x3) TALOS_TC_AUX(256, 3, false, 2)
-    else if (bn == 128) TALOS_TC_AUX(128, 2, true, 2)
-    else TALOS_TC_AUX(256, 2, true, 1)
+#define TALOS_TC_AUX(BNv, ST, X3v, SB, EWv)                                                                                         \
+  { const size_t smem = tc_smem_bytes<BNv, ST, X3v, SB, EWv>() + 128;                                                               \
+    TALOS_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_aux_kernel<BNv, ST, X3v, SB, EWv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    gemm_tc_aux_kernel<BNv, ST, X3v, SB, EWv><<<grid, TcRoles<X3v, X3v, BNv, EWv>::THREADS, smem, ctx->stream>>>(ta, tb, tc, tbl, tx, g); }
+    if (!x3) TALOS_TC_AUX(256, 3, false, 2, 0)
+    else if (bn == 128 && wide_epi) TALOS_TC_AUX(128, 2, true, 1, 16)
+    else if (bn == 128) TALOS_TC_AUX(128, 2, true, 2, 0)
+    else TALOS_TC_AUX(256, 2, true, 1, 0)
 #undef TALOS_TC_AUX
     talos_launched(ctx, "gemm_tcgen05");
     *extra->colsum_slabs_out = 4 * grid;
@@ -658,7 +664,8 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
     else if (x3) launch_major<BNv, ST3, true, 1, false, SB3>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);           \
     else launch_major<BNv, ST, false, 1, false, SB>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                    \
   }
-  if (short_k && presplit) launch_major<128, 2, true, 1, true, 2>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);
+  if (short_k && presplit && wide_epi) launch_major<128, 2, true, 1, true, 1, 16>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);
+  else if (short_k && presplit) launch_major<128, 2, true, 1, true, 2>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);
   else TALOS_TC_CASE(256, 3, 2, 2, 1) else TALOS_TC_CASE(128, 6, 1, 3, 1) else TALOS_TC_CASE(64, 8, 1, 4, 1) else TALOS_TC_CASE(32, 8, 2, 4, 2)
 #undef TALOS_TC_CASE
   if (splits > 1 && !keep_partials) talos_splitk_reduce(ctx, g.partial, splits, M, N, C, ldc, epi);

@@ -242,8 +242,9 @@ __device__ __forceinline__ float4 epilogue_group(float4 v, const float* __restri
 // tiles through memory.
 template <int BN, int EPI_WARPS = 8>
 __device__ __forceinline__ void tc_fold_chain(uint32_t t_run, uint32_t t_acc, int warp) {
-  const int quad = warp & 3, half = EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;
-  constexpr int HALF_COLS = (EPI_WARPS == 8 && BN >= 64) ? BN / 2 : BN;
+  constexpr int PARTS = EPI_WARPS / 4;                       // warps per TMEM lane quadrant: each takes BN / PARTS columns
+  const int quad = warp & 3, half = (warp - 2) >> 2;
+  constexpr int HALF_COLS = (PARTS > 1 && BN / PARTS >= 32) ? BN / PARTS : BN;
   const uint32_t row = (uint32_t)(quad * 32) << 16;
 #pragma unroll 1
   for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS && c0 < BN; c0 += 16) {
@@ -266,14 +267,15 @@ __device__ __forceinline__ void tc_fold_chain(uint32_t t_run, uint32_t t_acc, in
 template <int BN, int EPI_WARPS = 8, int SBUF = 1>
 __device__ __forceinline__ void tc_epilogue_tile(const TcArgs& g, const CUtensorMap* tmap_c, uint32_t t_base, int warp, int lane, float* stage,
                                                  long long m_base, int nb, int ks, int bz, uint32_t& store_count) {
-  static_assert(EPI_WARPS == 8 || EPI_WARPS == 4, "two warps per TMEM lane quadrant, or one");
+  static_assert(EPI_WARPS == 16 || EPI_WARPS == 8 || EPI_WARPS == 4, "four, two or one warp per TMEM lane quadrant");
   float* const c_base = g.C + (long long)bz * g.stride_c;   // this batch member's C (split-K never batches: ks or bz is 0)
   // Each warp drains its 32-lane quadrant (one accumulator row per lane) 32 columns at a time.
-  const int quad = warp & 3, half = EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;
+  constexpr int PARTS = EPI_WARPS / 4;
+  const int quad = warp & 3, half = (warp - 2) >> 2;          // (which of the quadrant's PARTS column shares)
   const long long m0 = m_base + quad * 32;
   const uint32_t t_row = t_base + ((uint32_t)(quad * 32) << 16);
   const int rows_valid = (int)min((long long)32, (long long)g.M - m0);
-  constexpr int HALF_COLS = (EPI_WARPS == 8 && BN >= 64) ? BN / 2 : BN;
+  constexpr int HALF_COLS = (PARTS > 1 && BN / PARTS >= 32) ? BN / PARTS : BN;
   const int c_begin = half * HALF_COLS, c_end = min((half + 1) * HALF_COLS, BN);
   if (rows_valid <= 0) return;
   if (g.tma_out) {
@@ -427,7 +429,7 @@ __device__ __forceinline__ void tc_aux_request(const CUtensorMap* tmap_aux, floa
   mbar_expect_tx(aux_bar, 32 * 32 * 4);
   tma_load_3d(buf, tmap_aux, n0, (int)m0, 0, aux_bar);
 }
-template <int BN, int SBUF>
+template <int BN, int SBUF, int EPI_WARPS = 8>
 __device__ __forceinline__ bool tc_epilogue_tile_aux(const TcArgs& g, const CUtensorMap* tmap_c, const CUtensorMap* tmap_aux, uint32_t t_base, int warp, int lane,
                                                      float* stage, uint64_t* aux_bar, volatile int* abort_flag, long long m_base, int nb,
                                                      bool next_valid, long long next_m_base, int next_nb, uint32_t& store_count, TcAuxState& st) {
@@ -435,7 +437,8 @@ __device__ __forceinline__ bool tc_epilogue_tile_aux(const TcArgs& g, const CUte
   const long long m0 = m_base + quad * 32;
   const uint32_t t_row = t_base + ((uint32_t)(quad * 32) << 16);
   const int rows_valid = (int)max(0LL, min((long long)32, (long long)g.M - m0));
-  constexpr int HALF_COLS = BN / 2, CHUNKS = HALF_COLS / 32;
+  constexpr int HALF_COLS = BN / (EPI_WARPS / 4), CHUNKS = HALF_COLS / 32;
+  static_assert(EPI_WARPS >= 8 && HALF_COLS >= 32, "a warp's share is whole 32-column chunks");
   if (next_valid && lane < CHUNKS && next_m_base + quad * 32 < g.M)   // the next tile's activation chunks: into L2 while this tile is worked on
     tma_prefetch_3d(tmap_aux, next_nb * BN + half * HALF_COLS + lane * 32, (int)(next_m_base + quad * 32), 0);
 #pragma unroll 1
