@@ -127,8 +127,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
         if (++pf_kb >= pf_kb1) { pf_it += gridDim.x; pf_decode(); }
       };
       const bool pf_on = g.pf_a || g.pf_b;
-      const bool b_resident = BPS && g.kb_total <= STAGES && STAGES % g.kb_total == 0 && g.n_tiles == 1 && g.batch == 1 && g.splits == 1;
-      int issued = 0;
+      const bool b_resident = BPS && g.kb_total <= STAGES && STAGES % g.kb_total == 0 && g.group_m >= g.m_tiles && g.batch == 1 && g.splits == 1;
+      int b_loads_left = 0, b_panel = -1;
       if (pf_on) { pf_decode(); for (int i = 0; i < PF_DIST; ++i) pf_step(); }
       for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
         const int bz = it / per_batch, r = it - bz * per_batch;
@@ -140,11 +140,13 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
           // Test hook: this stage is never armed nor loaded, so its consumers' bounded waits run out and the CTA
           // leaves through the abort path (nothing faults; the loads already in flight land and are ignored).
           if (g.dbg_skip_kb >= 0 && blockIdx.x == 0 && it == 0 && kb - kb0 == g.dbg_skip_kb) { if (++stage == STAGES) { stage = 0; phase ^= 1; } continue; }
-          // A product with a single column panel whose k-blocks divide the stage count (K = 32: the input gradient of the
-          // fused heads; K = 64 with two stages: the first layer) meets the SAME B tile every time it comes back to a
-          // stage: each stage's B buffers are filled on the stage's first use and kept.
-          const bool load_b = !b_resident || issued < STAGES;
-          ++issued;
+          // A product whose k-blocks divide the stage count (K = 32: the input gradient of the fused heads; K = 64 with
+          // two stages: the first layer) meets the SAME B tile every time it comes back to a stage for as long as it
+          // stays in one column panel, and the plain tile order walks a CTA through one panel after the other: each
+          // stage's B buffers are filled on the stage's first use in a panel and kept.
+          if (b_resident && kb == kb0 && nb != b_panel) { b_panel = nb; b_loads_left = STAGES; }
+          const bool load_b = !b_resident || b_loads_left > 0;
+          if (b_resident && b_loads_left > 0) --b_loads_left;
           mbar_expect_tx(full + stage, A_BYTES + (load_b ? B_BYTES + (BPS ? B_BYTES : 0) : 0));
           uint8_t* a_dst = sA + stage * A_BYTES; uint8_t* b_dst = sB + stage * B_STRIDE;
           if (BPS && load_b) {
