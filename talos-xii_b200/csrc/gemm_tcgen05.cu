@@ -663,6 +663,7 @@ void tc_launch(talos_ctx* ctx, int opA, int opB, int64_t M, int64_t N, int64_t K
 #define TALOS_TC_CASE(BNv, ST, SB, ST3, SB3)                                                                      \
   if (bn == BNv) {                                                                                                \
     if (x3 && presplit) launch_major<BNv, ST3, true, 1, true, SB3>(ctx, a_mn, b_mn, ta, tb, tc, tbl, g, grid);    \
+    else if (x3 && BNv == 256 && !getenv("TALOS_TC_NO_EPI8")) launch_major<BNv, ST3, true, 1, false, SB3, (BNv == 256 ? 8 : 0)>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid); \
     else if (x3) launch_major<BNv, ST3, true, 1, false, SB3>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);           \
     else launch_major<BNv, ST, false, 1, false, SB>(ctx, a_mn, b_mn, ta, tb, tc, tb, g, grid);                    \
   }
