@@ -36,14 +36,15 @@ namespace {
 // Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, then the epilogue warps, then (3xTF32) the converter
 // warps.  When both operands are split in the kernel (no pre-split B: the weight-gradient products, whose epilogue
 // runs once per 16 k-blocks) the converter is the busy role, so it gets eight warps and the epilogue four.
-// EW: epilogue warps when not 0 (16 for the K <= 64 configurations, which are all epilogue: four warps per TMEM lane
-// quadrant, one 32-column chunk of a 128-column tile each).
+// EW: epilogue warps when not 0: 16 for the K <= 64 configurations, which are all epilogue (four warps per TMEM lane
+// quadrant, one 32-column chunk of a 128-column tile each); 8 for the 256-column tiles that split both operands in the
+// kernel (one split-K item per CTA: nothing overlaps its chain fold and partial-tile store).
 template <bool X3, bool BPS, int BN = 256, int EW = 0> struct TcRoles {
   // (narrow tiles with a pre-split B are converter-bound too: their epilogue moves 32 or 64 columns a tile)
   static constexpr bool CONV_HEAVY = X3 && (!BPS || BN <= 64);
   static constexpr int EPI_WARPS = EW ? EW : (CONV_HEAVY ? 4 : 8);
   static constexpr int CONV_WARPS = X3 ? (CONV_HEAVY ? 8 : 4) : 0;
-  static constexpr int THREADS = (2 + EPI_WARPS + CONV_WARPS) * 32;       // 448 (3xTF32) or 320 (TF32)
+  static constexpr int THREADS = (2 + EPI_WARPS + CONV_WARPS) * 32;       // 448 (3xTF32) or 320 (TF32) by default; 576 / 704 with EW = 8 / 16
 };
 
 // SBUF: staging buffers per epilogue warp (2 where the configuration leaves the shared memory for it).
@@ -69,7 +70,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmap_a, const CU
   uint8_t* sB = sA + STAGES * A_BYTES;
   uint8_t* sAlo = sB + STAGES * B_STRIDE;
   uint8_t* sBlo = DUAL ? sB + B_BYTES : sAlo + (X3 ? STAGES * A_BYTES : 0);
-  float* stage_all = (float*)(sAlo + (X3 ? STAGES * A_BYTES : 0) + ((X3 && !DUAL) ? STAGES * B_BYTES : 0));   // 8 epilogue warps x 4 KB, 1024-byte aligned (TMA-store swizzle)
+  float* stage_all = (float*)(sAlo + (X3 ? STAGES * A_BYTES : 0) + ((X3 && !DUAL) ? STAGES * B_BYTES : 0));   // one 4 KB block per staging buffer of every epilogue warp (at least eight warps' worth), 1024-byte aligned (TMA-store swizzle)
   uint64_t* bars = (uint64_t*)(stage_all + STAGE_WARPS * 32 * 32 * SBUF);
   uint64_t* aux_bars = bars; bars += AUXT ? STAGE_WARPS : 0;                   // AUXT: one barrier per epilogue warp for its activation tiles
   uint64_t* full = bars;                   // TMA -> (converter | issuer)
